@@ -1,0 +1,414 @@
+/*
+ * CPU oracle for the mmaemu.scaled_mm hot path.  TEST INFRASTRUCTURE ONLY: it is the checker the parity tests,
+ * the smoke run and the CPU-baseline leg of the benchmark compare the CUDA path against; the product never calls it.
+ *
+ * It restates, in integer arithmetic, the algorithm of the reference (astding/mmaemu), function by function:
+ *   fp8_decode          mmaemu/formats.py:14-62, mmaemu/model/chain.py:202-214 (value, clamped exponent, zero rule)
+ *   block_fma           mmaemu/model/chain.py:84-104 (semantics) and 241-283 (fast exact form)
+ *   chain over K        mmaemu/model/chain.py:107-117, 286-332
+ *   plan walk           mmaemu/model/plan.py:62-136 (split layouts, slow chunks)
+ *   combine             mmaemu/model/plan.py:139-156, 169-208
+ *   non-finite class    mmaemu/model/specials.py:25-80
+ *   epilogue            mmaemu/model/epilogue.py:34-78
+ * Parity is pinned: oracle/pin_against_reference.py checks this file against the reference's Python model and against
+ * the reference's own golden vectors (toolbox instruction vectors, H100 live-call hashes, RTX 4060 recordings).
+ *
+ * Integer form of one block step (preset frac = frac_out = 13, early accumulator), proved equal to the float64
+ * model: with P = Ma * Mb the product of the integer significands (E4M3: 3 fraction bits, E5M2: 2), ep = ea + eb the
+ * sum of the clamped exponents, E = max(max over nonzero products of ep, exponent(c)), every term is expressed in
+ * units of 2^(E-13):  term = +-floor(P * 2^(ep - E + 13 - fa - fb)),  c_term = +-(mant24(c) >> (E - ec + 10));
+ * the exact integer sum S is truncated to 14 significant bits and the result is S * 2^(E-13); a zero sum is +0.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define FMT_E4M3 0
+#define FMT_E5M2 1
+#define OUT_F32 0
+#define OUT_BF16 1
+#define OUT_F16 2
+#define OUT_E4M3 3
+#define OUT_E5M2 4
+#define SCHEME_NONE 0
+#define SCHEME_SERIAL 1
+#define SCHEME_PAIRWISE 2
+#define SCHEME_CONTIGUOUS 3
+#define EXP_ZERO (-10000)
+#define MIN_EXP (-132)
+#define CANON_NAN32 0x7FFFFFFFu
+
+/* class of a code */
+#define CLS_FINITE 0
+#define CLS_NAN 1
+#define CLS_PINF 2
+#define CLS_NINF 3
+
+typedef struct {
+  int16_t mant; /* signed integer significand: E4M3 units 2^-3 (|m| <= 15), E5M2 units 2^-2 (|m| <= 7) */
+  int16_t exp;  /* clamped exponent (E4M3 >= -6, E5M2 >= -14); EXP_ZERO for zero and non-finite codes */
+  uint8_t cls;  /* CLS_* */
+  uint8_t neg;  /* sign bit of the code */
+} dec_t;
+
+static inline uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+/* formats.py:14-19, 47-62; chain.py:202-214: non-finite codes are sanitised to +0 before the chains
+ * (specials.py:25-30), zero codes never take part in the block maximum (chain.py:90). */
+static dec_t fp8_decode(uint8_t code, int fmt) {
+  dec_t d;
+  int mbits = fmt == FMT_E4M3 ? 3 : 2;
+  int bias = fmt == FMT_E4M3 ? 7 : 15;
+  int emin = fmt == FMT_E4M3 ? -6 : -14;
+  int e = (code & 0x7F) >> mbits;
+  int m = code & ((1 << mbits) - 1);
+  d.neg = code >> 7;
+  d.cls = CLS_FINITE;
+  if (fmt == FMT_E4M3) {
+    if ((code & 0x7F) == 0x7F) d.cls = CLS_NAN;
+  } else if (e == 31) {
+    d.cls = m ? CLS_NAN : (d.neg ? CLS_NINF : CLS_PINF);
+  }
+  if (d.cls != CLS_FINITE || (code & 0x7F) == 0) {
+    d.mant = 0;
+    d.exp = EXP_ZERO;
+    return d;
+  }
+  int mag = e ? ((1 << mbits) | m) : m; /* subnormals keep a denormalised significand at emin */
+  d.mant = (int16_t)(d.neg ? -mag : mag);
+  d.exp = (int16_t)(e ? e - bias : emin);
+  return d;
+}
+
+static inline int fmt_mbits(int fmt) { return fmt == FMT_E4M3 ? 3 : 2; }
+
+/* exponent(c) of an fp32 accumulator (normal or zero; the chains never produce fp32 subnormals, chain.py:193-197).
+ * Subnormal c (only reachable through the instruction-level entry) is handled like the float64 model: its true
+ * exponent. */
+static inline int f32_exp_mant(float c, uint32_t *mant24, int *neg) {
+  uint32_t u = f2u(c);
+  *neg = u >> 31;
+  int be = (u >> 23) & 0xFF;
+  uint32_t fr = u & 0x7FFFFF;
+  if (be == 0) {
+    if (fr == 0) { *mant24 = 0; return EXP_ZERO; }
+    int sh = 0;
+    while (!(fr & 0x800000)) { fr <<= 1; ++sh; }
+    *mant24 = fr;
+    return -126 - sh;
+  }
+  *mant24 = fr | 0x800000;
+  return be - 127;
+}
+
+/* One block-FMA step (chain.py:84-104): n products a[i] * b[i] plus c; returns the fp32 result. */
+static float block_fma(const dec_t *a, const dec_t *b, int n, float c, int fsum /* fa + fb fraction bits */) {
+  int E = EXP_ZERO;
+  for (int i = 0; i < n; ++i) {
+    if (a[i].mant != 0 && b[i].mant != 0) {
+      int ep = a[i].exp + b[i].exp;
+      if (ep > E) E = ep;
+    }
+  }
+  uint32_t cm; int cneg;
+  int ec = f32_exp_mant(c, &cm, &cneg);
+  if (ec > E) E = ec;
+  if (E < MIN_EXP) E = MIN_EXP;  /* presets.py:78-89 min_exp; unobservable for chains that start at +0 */
+  int64_t S = 0;
+  for (int i = 0; i < n; ++i) {
+    int32_t P = (int32_t)a[i].mant * (int32_t)b[i].mant;
+    if (P == 0) continue;
+    int s = a[i].exp + b[i].exp - E + 13 - fsum;
+    int64_t mag = P < 0 ? -(int64_t)P : (int64_t)P;
+    if (s >= 0) mag <<= s; else mag = (-s >= 32) ? 0 : (mag >> (-s)); /* truncation toward zero on the magnitude */
+    S += P < 0 ? -mag : mag;
+  }
+  if (cm) {
+    int sh = E - ec + 10; /* mant24 has 23 fraction bits; the grid has 13 */
+    int64_t mag = sh >= 32 ? 0 : ((int64_t)cm >> sh);
+    S += cneg ? -mag : mag;
+  }
+  if (S == 0) return 0.0f;
+  int neg = S < 0;
+  uint64_t m = (uint64_t)(neg ? -S : S);
+  int nb = 64 - __builtin_clzll(m);
+  int ed = E - 13 + nb - 1;                        /* exponent of the exact sum, clamped at -126 (chain.py:101) */
+  int drop = (ed < -126 ? -126 : ed) - E;          /* 13 fraction bits relative to that exponent */
+  if (drop > 0) m = drop >= 63 ? 0 : ((m >> drop) << drop);
+  if (m == 0) return 0.0f;
+  float r = ldexpf((float)m, E - 13);              /* exact: m < 2^24 and the result is a normal fp32 */
+  return neg ? -r : r;
+}
+
+/* Chain from +0 over the K indices [k0, k1) (zero padded to a multiple of nfma; indices >= K are zero codes). */
+static float chain_range(const dec_t *a, const dec_t *b, int K, int64_t k0, int64_t k1, int nfma, int fsum, float acc) {
+  static const dec_t zero = {0, EXP_ZERO, CLS_FINITE, 0};
+  dec_t ta[64], tb[64];
+  for (int64_t k = k0; k < k1; k += nfma) {
+    if (k >= K) break; /* an all-zero block leaves the accumulator unchanged */
+    int n = nfma;
+    if (k + n <= K && k + n <= k1) {
+      acc = block_fma(a + k, b + k, n, acc, fsum);
+    } else {
+      for (int i = 0; i < n; ++i) {
+        int in = (k + i < K) && (k + i < k1);
+        ta[i] = in ? a[k + i] : zero;
+        tb[i] = in ? b[k + i] : zero;
+      }
+      acc = block_fma(ta, tb, n, acc, fsum);
+    }
+  }
+  return acc;
+}
+
+typedef struct {
+  int nfma, fast, S, scheme;
+} plan_t;
+
+/* fp32 accumulator of one output under the plan (plan.py:82-136 layouts, 169-208 executor, 139-156 combine). */
+static float plan_output(const dec_t *a, const dec_t *b, int K, int fsum, const plan_t *p) {
+  int S = p->S < 1 ? 1 : p->S;
+  if (S == 1 && p->fast) return chain_range(a, b, K, 0, K, p->nfma, fsum, 0.0f);
+  float parts[64];
+  int contiguous = (S > 1 && p->scheme == SCHEME_CONTIGUOUS);
+  int W = contiguous ? 128 : 64;                     /* plan.py:43-46 */
+  int64_t T = ((int64_t)K + W - 1) / W;
+  int64_t q = (T + S - 1) / S;                       /* contiguous: tiles per split (plan.py:73-74) */
+  int group = p->fast ? 0 : (contiguous ? 1 : 2);    /* slow: own tiles per chain; 0 = all (plan.py:115-134) */
+  for (int s = 0; s < S; ++s) {
+    float part = 0.0f, acc = 0.0f;
+    int in_chain = 0, any = 0;
+    int64_t t_begin = contiguous ? (s * q < T ? s * q : T) : s;
+    int64_t t_end = contiguous ? ((s + 1) * q < T ? (s + 1) * q : T) : T;
+    int64_t t_step = contiguous ? 1 : S;
+    for (int64_t t = t_begin; t < t_end; t += t_step) {
+      acc = chain_range(a, b, K, t * W, (t + 1) * W, p->nfma, fsum, acc);
+      any = 1;
+      if (group && ++in_chain == group) {
+        part = part + acc; /* fp32 round-to-nearest, serially from +0 (plan.py:198-201) */
+        acc = 0.0f;
+        in_chain = 0;
+      }
+    }
+    if (!group) part = any ? acc : 0.0f;             /* one chain per split; an empty split is +0 */
+    else if (in_chain) part = part + acc;
+    parts[s] = part;
+  }
+  if (p->scheme == SCHEME_PAIRWISE) {                /* plan.py:149-155 */
+    int h = (S + 1) / 2;
+    float r = parts[S - 1];
+    for (int i = 0; i < h; ++i) {
+      float slot = (i + h < S - 1) ? parts[i] + parts[i + h] : parts[i];
+      r = r + slot;
+    }
+    return r;
+  }
+  float r = parts[0];
+  for (int s = 1; s < S; ++s) r = r + parts[s];
+  return r;
+}
+
+/* IEEE class of sum_k a[k] * b[k] when the row or the column holds a non-finite code (specials.py:33-53):
+ * returns 0 if the sum is finite, else writes the fp32 bits. */
+static int nonfinite_value(const dec_t *a, const dec_t *b, int K, uint32_t *bits) {
+  int nan = 0, pos = 0, neg = 0;
+  for (int k = 0; k < K; ++k) {
+    int ca = a[k].cls, cb = b[k].cls;
+    if (ca == CLS_FINITE && cb == CLS_FINITE) continue;
+    if (ca == CLS_NAN || cb == CLS_NAN) { nan = 1; continue; }
+    int a_inf = ca != CLS_FINITE, b_inf = cb != CLS_FINITE;
+    int a_zero = !a_inf && a[k].mant == 0, b_zero = !b_inf && b[k].mant == 0;
+    if ((a_inf && b_zero) || (b_inf && a_zero)) { nan = 1; continue; }
+    int sa = a_inf ? (ca == CLS_NINF) : a[k].neg;
+    int sb = b_inf ? (cb == CLS_NINF) : b[k].neg;
+    if (sa ^ sb) neg = 1; else pos = 1;
+  }
+  if (nan || (pos && neg)) { *bits = CANON_NAN32; return 1; }
+  if (pos) { *bits = 0x7F800000u; return 1; }
+  if (neg) { *bits = 0xFF800000u; return 1; }
+  return 0;
+}
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * epilogue (epilogue.py:43-78) */
+static inline float rn32_mul(float x, float y) { return (float)((double)x * (double)y); } /* exact product, 1 rounding */
+
+static uint16_t f32_to_bf16(float f) {
+  uint32_t u = f2u(f);
+  if ((u & 0x7FFFFFFF) > 0x7F800000u) return 0x7FFF;
+  uint32_t r = u + 0x7FFF + ((u >> 16) & 1); /* RNE on the low 16 bits; overflow rounds to Inf */
+  return (uint16_t)(r >> 16);
+}
+
+static uint16_t f32_to_f16(float f) {
+  uint32_t u = f2u(f);
+  uint32_t sign = (u >> 16) & 0x8000, x = u & 0x7FFFFFFF;
+  if (x > 0x7F800000u) return 0x7FFF;
+  if (x >= 0x47800000u) return (uint16_t)(sign | 0x7C00); /* >= 2^16 (also Inf): Inf; 65520 rounds up below */
+  if (x >= 0x38800000u) {                                  /* normal half range (>= 2^-14) */
+    uint32_t m = x - 0x38000000u;                          /* rebias 127 -> 15 */
+    uint32_t r = m + 0xFFF + ((m >> 13) & 1);
+    return (uint16_t)(sign | (r >> 13));                   /* carries into Inf correctly */
+  }
+  if (x < 0x33000000u) return (uint16_t)sign;              /* < 2^-25: rounds to zero (2^-25 itself ties to even 0) */
+  int e = (int)(x >> 23);                                  /* biased fp32 exponent, 102..112 */
+  uint32_t m = (x & 0x7FFFFF) | 0x800000;
+  int sh = 126 - e;                                        /* value = m * 2^(e-150); half subnormal unit 2^-24 */
+  uint32_t q = m >> sh, rem = m & ((1u << sh) - 1), half = 1u << (sh - 1);
+  if (rem > half || (rem == half && (q & 1))) ++q;
+  return (uint16_t)(sign | q);
+}
+
+/* fp32 -> fp8 with saturation to +-max (Inf included), NaN -> 0x7F, RNE (epilogue.py:52-58). */
+static uint8_t f32_to_fp8(float f, int fmt) {
+  uint32_t u = f2u(f);
+  uint32_t sign = (u >> 24) & 0x80, x = u & 0x7FFFFFFF;
+  if (x > 0x7F800000u) return 0x7F;
+  int mbits = fmt_mbits(fmt), bias = fmt == FMT_E4M3 ? 7 : 15;
+  uint32_t maxcode = fmt == FMT_E4M3 ? 0x7E : 0x7B;
+  float maxval = fmt == FMT_E4M3 ? 448.0f : 57344.0f;
+  if (u2f(x) >= maxval) return (uint8_t)(sign | maxcode);
+  int e = (int)(x >> 23) - 127;
+  int emin = 1 - bias;
+  uint32_t m = (x & 0x7FFFFF) | 0x800000;
+  if (x < 0x00800000u) return (uint8_t)sign; /* fp32 subnormals are far below every fp8 subnormal */
+  int sh, eb;
+  if (e >= emin) { sh = 23 - mbits; eb = e + bias; } else { sh = 23 - mbits + (emin - e); eb = 0; }
+  if (sh > 31) return (uint8_t)sign;
+  uint32_t q = m >> sh, rem = m & ((1u << sh) - 1), half = 1u << (sh - 1);
+  if (rem > half || (rem == half && (q & 1))) ++q;
+  uint32_t code;
+  if (eb > 0) code = ((uint32_t)(eb - 1) << mbits) + q; /* q includes the hidden bit: carries propagate to exponent */
+  else code = q;
+  if (code > maxcode) code = maxcode;
+  return (uint8_t)(sign | code);
+}
+
+static void store_out(void *D, int64_t idx, int out_dtype, float acc, float alpha, const float *scale_result) {
+  float y = (float)((double)acc * (double)alpha + 0.0); /* fma(acc, alpha, +0): one rounding (epilogue.py:76-77) */
+  switch (out_dtype) {
+    case OUT_F32: {
+      uint32_t u = f2u(y);
+      if ((u & 0x7FFFFFFF) > 0x7F800000u) u = CANON_NAN32;
+      ((uint32_t *)D)[idx] = u;
+      break;
+    }
+    case OUT_BF16: ((uint16_t *)D)[idx] = f32_to_bf16(y); break;
+    case OUT_F16: ((uint16_t *)D)[idx] = f32_to_f16(y); break;
+    default: {
+      if (scale_result) y = rn32_mul(y, *scale_result);
+      ((uint8_t *)D)[idx] = f32_to_fp8(y, out_dtype == OUT_E4M3 ? FMT_E4M3 : FMT_E5M2);
+    }
+  }
+}
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * exported entry points */
+
+static dec_t *decode_matrix(const uint8_t *X, int64_t ld, int rows, int K, int fmt, uint8_t *row_nonfinite) {
+  dec_t lut[256];
+  for (int c = 0; c < 256; ++c) lut[c] = fp8_decode((uint8_t)c, fmt);
+  dec_t *out = (dec_t *)malloc(sizeof(dec_t) * (size_t)rows * (size_t)(K > 0 ? K : 1));
+  if (!out) return NULL;
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    uint8_t nf = 0;
+    for (int k = 0; k < K; ++k) {
+      dec_t d = lut[X[(size_t)r * ld + k]];
+      out[(size_t)r * K + k] = d;
+      nf |= d.cls != CLS_FINITE;
+    }
+    row_nonfinite[r] = nf;
+  }
+  return out;
+}
+
+/* fp32 accumulator [M, N] (ldc floats per row) of A [M, K] x B [N, K]^T under the plan, before alpha
+ * (mmaemu.accumulate, api.py:382-421; execute_plan, plan.py:169-208). Returns 0, or -1 on a bad argument. */
+int oracle_accumulate(const uint8_t *A, int64_t lda, int fmt_a, const uint8_t *B, int64_t ldb, int fmt_b, float *C,
+                      int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme, int nthreads) {
+  if (M < 0 || N < 0 || K < 0 || nfma < 1 || nfma > 64 || S < 1 || S > 64) return -1;
+  if (M == 0 || N == 0) return 0;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+  uint8_t *nfa = (uint8_t *)calloc((size_t)M + 1, 1), *nfb = (uint8_t *)calloc((size_t)N + 1, 1);
+  dec_t *da = decode_matrix(A, lda, M, K, fmt_a, nfa), *db = decode_matrix(B, ldb, N, K, fmt_b, nfb);
+  if (!da || !db || !nfa || !nfb) { free(da); free(db); free(nfa); free(nfb); return -1; }
+  plan_t p = {nfma, fast, S, scheme};
+  int fsum = fmt_mbits(fmt_a) + fmt_mbits(fmt_b);
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int m = 0; m < M; ++m) {
+    const dec_t *a = da + (size_t)m * K;
+    for (int n = 0; n < N; ++n) {
+      const dec_t *b = db + (size_t)n * K;
+      float acc = K ? plan_output(a, b, K, fsum, &p) : 0.0f;
+      uint32_t bits;
+      if ((nfa[m] | nfb[n]) && nonfinite_value(a, b, K, &bits)) acc = u2f(bits);
+      C[(size_t)m * ldc + n] = acc;
+    }
+  }
+  free(da); free(db); free(nfa); free(nfb);
+  return 0;
+}
+
+/* The whole call: accumulator, then epilogue into D [M, N] of out_dtype (ldd elements per row)
+ * (api.py:329-346). scale_result may be NULL. */
+int oracle_scaled_mm(const uint8_t *A, int64_t lda, int fmt_a, const uint8_t *B, int64_t ldb, int fmt_b, void *D,
+                     int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                     float scale_a, float scale_b, const float *scale_result, int nthreads) {
+  if (out_dtype < OUT_F32 || out_dtype > OUT_E5M2) return -1;
+  if (M <= 0 || N <= 0) return M < 0 || N < 0 ? -1 : 0;
+  float *C = (float *)malloc(sizeof(float) * (size_t)M * (size_t)N);
+  if (!C) return -1;
+  int rc = oracle_accumulate(A, lda, fmt_a, B, ldb, fmt_b, C, N, M, N, K, nfma, fast, S, scheme, nthreads);
+  if (rc == 0) {
+    float alpha = rn32_mul(scale_a, scale_b);
+#pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+      for (int n = 0; n < N; ++n)
+        store_out(D, (int64_t)m * ldd + n, out_dtype, C[(size_t)m * N + n], alpha, scale_result);
+  }
+  free(C);
+  return rc;
+}
+
+/* Epilogue alone on an fp32 accumulator array (epilogue.py:65-78), count elements. */
+int oracle_epilogue(const float *acc, void *D, int out_dtype, int64_t count, float scale_a, float scale_b,
+                    const float *scale_result) {
+  if (out_dtype < OUT_F32 || out_dtype > OUT_E5M2) return -1;
+  float alpha = rn32_mul(scale_a, scale_b);
+  for (int64_t i = 0; i < count; ++i) store_out(D, i, out_dtype, acc[i], alpha, scale_result);
+  return 0;
+}
+
+/* Instruction-level chain d = chain(a * b) from c over the last dimension (mmaemu.model.dot, chain.py:145-182):
+ * a, b: [rows, K] codes, c: [rows] fp32 start values, d: [rows] results. */
+int oracle_dot(const uint8_t *a, int fmt_a, const uint8_t *b, int fmt_b, const float *c, float *d, int rows, int K,
+               int nfma) {
+  if (nfma < 1 || nfma > 64) return -1;
+  dec_t la[256], lb[256];
+  for (int i = 0; i < 256; ++i) { la[i] = fp8_decode((uint8_t)i, fmt_a); lb[i] = fp8_decode((uint8_t)i, fmt_b); }
+  int fsum = fmt_mbits(fmt_a) + fmt_mbits(fmt_b);
+  dec_t *ta = (dec_t *)malloc(sizeof(dec_t) * (size_t)(K + 64)), *tb = (dec_t *)malloc(sizeof(dec_t) * (size_t)(K + 64));
+  if (!ta || !tb) { free(ta); free(tb); return -1; }
+  for (int r = 0; r < rows; ++r) {
+    for (int k = 0; k < K; ++k) { ta[k] = la[a[(size_t)r * K + k]]; tb[k] = lb[b[(size_t)r * K + k]]; }
+    d[r] = chain_range(ta, tb, K, 0, K, nfma, fsum, c ? c[r] : 0.0f);
+  }
+  free(ta); free(tb);
+  return 0;
+}
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
