@@ -1,0 +1,110 @@
+/*
+ * mmaemu_b200 -- C ABI of the B200 (sm_100a) backend for the mmaemu.scaled_mm hot path.
+ *
+ * Every function is a host function of libmmaemu_b200.so. Pointers named *_dev are device pointers owned by the
+ * caller; nothing is allocated internally unless a function says so. All launches are asynchronous on the given
+ * cudaStream_t (passed as void*; NULL = the legacy default stream). Functions return MMB200_OK (0) or a negative
+ * status, never throw and never abort. The library holds no mutable global state apart from per-device function
+ * attributes that are set once.
+ *
+ * Operands are FP8 code bytes: A is [M, K] row-major with leading dimension lda (bytes), B is [N, K] row-major with
+ * leading dimension ldb -- that is mat2.t() of torch._scaled_mm's column-major [K, N] operand.
+ *
+ * What each entry point replaces in the reference (astding/mmaemu, paths relative to its root):
+ *   mmb200_chain       the kernel ABI v1 entry points mmaemu_{h4,h1,v4,v1}_e4m3e4m3 (mmaemu/backends/cuda/spec.py:3-16)
+ *                      together with their launch wrapper chain_fn_for (mmaemu/backends/cuda/kernels.py:85-134);
+ *   mmb200_scaled_mm   the compute lines of _scaled_mm_impl (mmaemu/api.py:342-346): execute_plan
+ *                      (mmaemu/model/plan.py:169-208: sanitise, per-chunk gathers and launches, slow-accumulation and
+ *                      split-K combination, non-finite patch) and epilogue.apply (mmaemu/model/epilogue.py:65-78),
+ *                      fused into one launch;
+ *   mmb200_accumulate  execute_plan alone, as mmaemu.accumulate uses it (mmaemu/api.py:382-421);
+ *   mmb200_scaled_mm_host   the same call for callers that hold host memory (no reference counterpart below the
+ *                      Python level: the reference moves tensors with torch).
+ */
+#ifndef MMAEMU_B200_H
+#define MMAEMU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MMB200_ABI_VERSION 1
+
+/* status codes */
+#define MMB200_OK 0
+#define MMB200_ERR_BAD_ARG (-1)       /* NULL pointer, negative size, unknown enum, ld < K, misaligned operand */
+#define MMB200_ERR_UNSUPPORTED (-2)   /* valid request this build has no kernel for */
+#define MMB200_ERR_ARCH (-3)          /* the current device is not sm_100 (the fatbin holds sm_100a code only) */
+#define MMB200_ERR_LAUNCH (-4)        /* the CUDA runtime refused the launch or a copy (see mmb200_last_cuda_error) */
+#define MMB200_ERR_TOO_LARGE (-5)     /* a size is beyond a documented limit */
+
+/* FP8 operand formats (mmaemu/formats.py:14-19) */
+#define MMB200_FMT_E4M3 0
+#define MMB200_FMT_E5M2 1
+
+/* output dtypes, numbered like the reference's split-K tables (mmaemu/platform/splitk_table.py OUT_CODES) */
+#define MMB200_OUT_F32 0
+#define MMB200_OUT_BF16 1
+#define MMB200_OUT_F16 2
+#define MMB200_OUT_E4M3 3
+#define MMB200_OUT_E5M2 4
+
+/* split-K reduction schemes (mmaemu/model/plan.py:46) */
+#define MMB200_SCHEME_NONE 0
+#define MMB200_SCHEME_SERIAL 1
+#define MMB200_SCHEME_PAIRWISE 2
+#define MMB200_SCHEME_CONTIGUOUS 3
+
+/* kernel families */
+#define MMB200_KERNEL_AUTO 0     /* the fastest kernel that serves the request */
+#define MMB200_KERNEL_INTEGER 1  /* pure-integer block model: every format pair and plan */
+#define MMB200_KERNEL_FAST 2     /* fp32 round-toward-zero FMA chain with integer corrections */
+
+#define MMB200_MAX_SPLITS 64
+
+int mmb200_abi_version(void);
+const char *mmb200_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+const char *mmb200_last_cuda_error(void);
+/* MMB200_OK if `device` can run the kernels, MMB200_ERR_ARCH otherwise. Does not change the current device. */
+int mmb200_device_supported(int device);
+
+/* C[m][n] = chain over k = 0..K-1 of A[m][k] * B[n][k] from +0 under the preset with `nfma` products per block
+ * (16 = ada, 32 = hopper); fp32 result, ldc in floats. Non-finite codes count as +0 (the caller sanitises, as
+ * execute_plan does). K need not be a multiple of nfma (the tail is zero padded). */
+int mmb200_chain(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b, float *C_dev,
+                 int64_t ldc, int M, int N, int K, int nfma, int kernel, void *stream);
+
+/* fp32 accumulator before alpha under the plan (nfma, fast, S, scheme), with the IEEE non-finite patch and canonical
+ * NaN. S = 1 ignores the scheme. */
+int mmb200_accumulate(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
+                      float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                      int kernel, void *stream);
+
+/* The whole call: plan, combination, non-finite patch, then alpha = RN32(scale_a * scale_b),
+ * y = RN32(fma(acc, alpha, +0)), conversion to out_dtype (fp8 outputs: optional scale_result multiply, saturation),
+ * canonical NaN. D is [M, N] row-major of out_dtype with leading dimension ldd (elements). The three scales are
+ * device pointers to one fp32 each (scale_result_dev may be NULL); they are read by the kernel, never by the host. */
+int mmb200_scaled_mm(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b, void *D_dev,
+                     int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                     const float *scale_a_dev, const float *scale_b_dev, const float *scale_result_dev, int kernel,
+                     void *stream);
+
+/* Same computation for HOST operands and a HOST result: copies A and B to the current device, runs the kernel, copies
+ * D back and waits for it. Device staging memory comes from the stream-ordered allocator (cudaMallocAsync) and is
+ * released before returning. Host buffers should be pinned for full copy speed but need not be. */
+int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void *B_host, int64_t ldb, int fmt_b,
+                          void *D_host, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
+                          int scheme, float scale_a, float scale_b, const float *scale_result /* host, nullable */,
+                          int kernel, void *stream);
+
+/* Number of kernel launches the library has issued in this process (all threads), for launch accounting. */
+int64_t mmb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MMAEMU_B200_H */

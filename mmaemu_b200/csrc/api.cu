@@ -1,0 +1,186 @@
+// Host side of the C ABI (include/mmaemu_b200.h): argument checks, kernel choice, launches. No allocation except in
+// mmb200_scaled_mm_host, which stages host operands through the stream-ordered allocator.
+#include <atomic>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+std::atomic<long long> g_launches{0};
+
+int cuda_fail(cudaError_t err) {
+  const char* s = cudaGetErrorString(err);
+  std::strncpy(g_cuda_error, s ? s : "unknown CUDA error", sizeof(g_cuda_error) - 1);
+  g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+  return MMB200_ERR_LAUNCH;
+}
+
+bool fmt_ok(int f) { return f == MMB200_FMT_E4M3 || f == MMB200_FMT_E5M2; }
+
+int current_device_ok() {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return cuda_fail(err);
+  return mmb200_device_supported(dev);
+}
+
+// Shared argument validation and dispatch of the three device-pointer entry points.
+int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D, int64_t ldd,
+        int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme, const float* sa, const float* sb,
+        const float* sr, int epilogue, int patch, int kernel, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
+  if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
+  if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
+  if (nfma != 16 && nfma != 32) return MMB200_ERR_UNSUPPORTED;
+  if (S < 1 || scheme < MMB200_SCHEME_NONE || scheme > MMB200_SCHEME_CONTIGUOUS) return MMB200_ERR_BAD_ARG;
+  if (S > 1 && scheme == MMB200_SCHEME_NONE) return MMB200_ERR_BAD_ARG;
+  if (S > MMB200_MAX_SPLITS) return MMB200_ERR_TOO_LARGE;
+  if (kernel < MMB200_KERNEL_AUTO || kernel > MMB200_KERNEL_FAST) return MMB200_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return MMB200_OK;
+  if (!D || ldd < N) return MMB200_ERR_BAD_ARG;
+  if (K > 0 && (!A || !B || lda < K || ldb < K)) return MMB200_ERR_BAD_ARG;
+  if (K >= (1 << 24)) return MMB200_ERR_TOO_LARGE;   // fp32 holds the non-finite term counts and block exponents
+  int rc = current_device_ok();
+  if (rc != MMB200_OK) return rc;
+
+  mmb::Params p;
+  std::memset(&p, 0, sizeof(p));
+  p.A = static_cast<const uint8_t*>(A);
+  p.B = static_cast<const uint8_t*>(B);
+  p.D = D;
+  p.scale_a = sa;
+  p.scale_b = sb;
+  p.scale_result = sr;
+  p.lda = lda; p.ldb = ldb; p.ldd = ldd;
+  p.M = M; p.N = N; p.K = K;
+  p.fmt_a = fmt_a; p.fmt_b = fmt_b; p.out_dtype = out_dtype;
+  p.fast = fast ? 1 : 0;
+  p.S = S;
+  p.scheme = S > 1 ? scheme : MMB200_SCHEME_NONE;
+  p.epilogue = epilogue;
+  p.patch_nonfinite = patch;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t err;
+  if (kernel == MMB200_KERNEL_FAST) {
+    if (!mmb::fast_supports(p, nfma)) return MMB200_ERR_UNSUPPORTED;
+    err = mmb::launch_fast(p, nfma, st);
+  } else if (kernel == MMB200_KERNEL_AUTO && mmb::fast_supports(p, nfma)) {
+    err = mmb::launch_fast(p, nfma, st);
+  } else {
+    err = mmb::launch_integer(p, nfma, st);
+  }
+  if (err != cudaSuccess) return cuda_fail(err);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MMB200_OK;
+}
+
+size_t out_size(int out_dtype) {
+  return out_dtype == MMB200_OUT_F32 ? 4 : (out_dtype <= MMB200_OUT_F16 ? 2 : 1);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mmb200_abi_version(void) { return MMB200_ABI_VERSION; }
+
+const char* mmb200_status_string(int status) {
+  switch (status) {
+    case MMB200_OK: return "ok";
+    case MMB200_ERR_BAD_ARG: return "bad argument";
+    case MMB200_ERR_UNSUPPORTED: return "unsupported request";
+    case MMB200_ERR_ARCH: return "the device is not sm_100 (this library holds sm_100a kernels only)";
+    case MMB200_ERR_LAUNCH: return "CUDA runtime error (see mmb200_last_cuda_error)";
+    case MMB200_ERR_TOO_LARGE: return "size beyond a documented limit";
+    default: return "unknown status";
+  }
+}
+
+const char* mmb200_last_cuda_error(void) { return g_cuda_error; }
+
+int mmb200_device_supported(int device) {
+  int major = 0;
+  cudaError_t err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (err != cudaSuccess) return cuda_fail(err);
+  int minor = 0;
+  err = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+  if (err != cudaSuccess) return cuda_fail(err);
+  return (major == 10 && minor == 0) ? MMB200_OK : MMB200_ERR_ARCH;
+}
+
+int mmb200_chain(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, float* C, int64_t ldc,
+                 int M, int N, int K, int nfma, int kernel, void* stream) {
+  return run(A, lda, fmt_a, B, ldb, fmt_b, C, ldc, MMB200_OUT_F32, M, N, K, nfma, 1, 1, MMB200_SCHEME_NONE, nullptr,
+             nullptr, nullptr, 0, 0, kernel, stream);
+}
+
+int mmb200_accumulate(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, float* C,
+                      int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme, int kernel,
+                      void* stream) {
+  return run(A, lda, fmt_a, B, ldb, fmt_b, C, ldc, MMB200_OUT_F32, M, N, K, nfma, fast, S, scheme, nullptr, nullptr,
+             nullptr, 0, 1, kernel, stream);
+}
+
+int mmb200_scaled_mm(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
+                     int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                     const float* scale_a, const float* scale_b, const float* scale_result, int kernel,
+                     void* stream) {
+  if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
+  return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
+             scale_result, 1, 1, kernel, stream);
+}
+
+int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
+                          int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                          float scale_a, float scale_b, const float* scale_result, int kernel, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
+  if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return MMB200_OK;
+  if (!D || ldd < N || (K > 0 && (!A || !B || lda < K || ldb < K))) return MMB200_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t es = out_size(out_dtype);
+  const size_t kpad = ((size_t)K + 15) / 16 * 16;       // dense device copies with a 16-byte aligned row stride
+  const size_t a_bytes = (size_t)M * kpad, b_bytes = (size_t)N * kpad, d_bytes = (size_t)M * N * es;
+  uint8_t* buf = nullptr;
+  const size_t a_off = 0, b_off = (a_bytes + 255) / 256 * 256, d_off = b_off + (b_bytes + 255) / 256 * 256;
+  const size_t s_off = d_off + (d_bytes + 255) / 256 * 256, total = s_off + 256;
+  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&buf), total, st);
+  if (err != cudaSuccess) return cuda_fail(err);
+  int rc = MMB200_OK;
+  float scales[3] = {scale_a, scale_b, scale_result ? *scale_result : 1.0f};
+  do {
+    if (K > 0) {
+      if (kpad != (size_t)K) {
+        err = cudaMemsetAsync(buf, 0, b_off + b_bytes, st);
+        if (err != cudaSuccess) break;
+      }
+      err = cudaMemcpy2DAsync(buf + a_off, kpad, A, (size_t)lda, (size_t)K, (size_t)M, cudaMemcpyHostToDevice, st);
+      if (err != cudaSuccess) break;
+      err = cudaMemcpy2DAsync(buf + b_off, kpad, B, (size_t)ldb, (size_t)K, (size_t)N, cudaMemcpyHostToDevice, st);
+      if (err != cudaSuccess) break;
+    }
+    err = cudaMemcpyAsync(buf + s_off, scales, sizeof(scales), cudaMemcpyHostToDevice, st);
+    if (err != cudaSuccess) break;
+    const float* sdev = reinterpret_cast<const float*>(buf + s_off);
+    rc = mmb200_scaled_mm(buf + a_off, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, buf + d_off, N,
+                          out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1, scale_result ? sdev + 2 : nullptr,
+                          kernel, stream);
+    if (rc != MMB200_OK) break;
+    err = cudaMemcpy2DAsync(D, (size_t)ldd * es, buf + d_off, (size_t)N * es, (size_t)N * es, (size_t)M,
+                            cudaMemcpyDeviceToHost, st);
+  } while (0);
+  cudaError_t ferr = cudaFreeAsync(buf, st);
+  cudaError_t serr = cudaStreamSynchronize(st);   // the scales array and the caller's buffers must outlive the copies
+  if (rc != MMB200_OK) return rc;
+  if (err != cudaSuccess) return cuda_fail(err);
+  if (ferr != cudaSuccess) return cuda_fail(ferr);
+  if (serr != cudaSuccess) return cuda_fail(serr);
+  return MMB200_OK;
+}
+
+int64_t mmb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"
