@@ -1,0 +1,417 @@
+"""Public entry points: scaled_mm, accumulate, explain -- the reference's call signatures on the B200 kernels.
+
+`scaled_mm` takes torch._scaled_mm's argument list (torch 2.7.1, `self` exposed as `input`) plus `profile=`,
+`splitk=` and `backend=`, validates the call exactly as the reference does, resolves the split-K decision of the
+emulated platform, and then makes ONE call into libmmaemu_b200.so that runs the accumulation plan, the non-finite
+patch and the epilogue in a single kernel. There is no CPU path: CPU tensors raise BackendUnavailableError once the
+call is otherwise valid.
+
+Validation order (normative in the reference, astding/mmaemu mmaemu/api.py:8-23, 280-326; the exception classes and
+the raise / no-raise outcome are what its parity tests pin):
+  1. Python argument types                                   TypeError
+  2. torch 2.7.1 _scaled_mm argument checks                  ReferenceRejectsError
+     zero-size results return here (M or N == 0: empty; K == 0: +0), then the cuBLASLt checks: operand layouts,
+     FP8 kinds, output dtype, 16-byte alignment, leading dimensions % 16
+  3. profile rejects (e4m3 x e4m3 -> e5m2)                   ReferenceRejectsError
+  4. scope: bias, row-wise scales, requires_grad             UnsupportedFeatureError
+  5. maturity warning of the profile                         ExperimentalPresetWarning
+  6. split-K resolution                                      SplitKUnknownError / ValueError
+  7. backend: device and library                             BackendUnavailableError
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import warnings
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _lib
+from .errors import (BackendUnavailableError, ExperimentalPresetWarning, ReferenceRejectsError,
+                     UnsupportedFeatureError)
+from .formats import E4M3, E5M2, OUT_DTYPE_NAMES, fmt_of, is_fp8_dtype
+from .numerics import check_plan, get_preset
+from .platforms import get_profile, profile_maturity_warning
+from .splitk import resolve_splitk
+
+__all__ = ["scaled_mm", "accumulate", "explain", "CallPlan", "BACKEND_NAMES"]
+
+BACKEND_NAMES = ("auto", "cuda", "cuda:b200", "cuda:b200-integer", "cuda:b200-fast")
+_KERNEL_OF = {"auto": "auto", "cuda": "auto", "cuda:b200": "auto", "cuda:b200-integer": "integer",
+              "cuda:b200-fast": "fast"}
+# dtypes torch 2.7.1 lets through its "is a float8 matrix" check before the zero-size early return
+_TORCH_FLOAT8 = {getattr(torch, n) for n in ("float8_e4m3fn", "float8_e5m2", "float8_e4m3fnuz", "float8_e5m2fnuz",
+                                             "float8_e8m0fnu") if hasattr(torch, n)}
+_warned_profiles: set = set()
+
+
+@dataclass
+class CallPlan:
+    """What a scaled_mm call would do (returned by explain)."""
+    validation: object = "ok"            # "ok" or (error class name, message)
+    profile: str = ""
+    preset: str = ""
+    preset_maturity: str = ""
+    split: object = None                 # SplitDecision | None
+    backend: str = ""
+    fallbacks: list = field(default_factory=list)
+    warnings: list = field(default_factory=list)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# layout predicates (as torch 2.7.1 hands matrices to cuBLASLt)
+def _row_major(t) -> bool:
+    return t.is_contiguous() or (t.stride(1) == 1 and t.stride(0) >= max(1, t.shape[1]))
+
+
+def _col_major(t) -> bool:
+    return not t.is_contiguous() and t.stride(0) == 1 and t.stride(1) >= max(1, t.shape[0])
+
+
+def _misaligned(t) -> bool:
+    if t.device.type == "cuda":
+        return t.data_ptr() % 16 != 0
+    return (t.storage_offset() * t.element_size()) % 16 != 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def _check_argument_types(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out):
+    required = (("input", input), ("mat2", mat2), ("scale_a", scale_a), ("scale_b", scale_b))
+    optional = (("bias", bias), ("scale_result", scale_result), ("out", out))
+    for name, v in required:
+        if not isinstance(v, torch.Tensor):
+            raise TypeError(f"scaled_mm(): argument '{name}' must be Tensor, not {type(v).__name__}")
+    for name, v in optional:
+        if v is not None and not isinstance(v, torch.Tensor):
+            raise TypeError(f"scaled_mm(): argument '{name}' must be Tensor, not {type(v).__name__}")
+    if out_dtype is not None and not isinstance(out_dtype, torch.dtype):
+        raise TypeError(f"scaled_mm(): argument 'out_dtype' must be torch.dtype, not {type(out_dtype).__name__}")
+    if type(use_fast_accum) is not bool:
+        raise TypeError(f"scaled_mm(): argument 'use_fast_accum' must be bool, not {type(use_fast_accum).__name__}")
+
+
+def _check_like_torch(mat1, mat2, scale_a, scale_b, bias, scale_result, out_dtype, out):
+    """The argument checks of torch 2.7.1's _scaled_mm_out_cuda, in its order. Returns (scaling kind, out dtype)."""
+    def reject(msg):
+        raise ReferenceRejectsError(msg)
+    if mat1.dim() != 2:
+        reject("mat1 must be a matrix")
+    if mat2.dim() != 2:
+        reject("mat2 must be a matrix")
+    if mat1.shape[1] != mat2.shape[0]:
+        reject(f"mat1 and mat2 shapes cannot be multiplied ({mat1.shape[0]}x{mat1.shape[1]} and "
+               f"{mat2.shape[0]}x{mat2.shape[1]})")
+    M, N = mat1.shape[0], mat2.shape[1]
+    if scale_a.dtype != torch.float32 or scale_b.dtype != torch.float32:
+        reject("Both scale_a and scale_b must be float (fp32) tensors.")
+    if scale_a.numel() == 1 and scale_b.numel() == 1:
+        scaling = "tensorwise"
+    elif scale_a.dim() != 2 or scale_b.dim() != 2:
+        reject("For non-TensorWise scaling, scale tensors must be 2-dimensional")
+    elif tuple(scale_a.shape) == (M, 1) and tuple(scale_b.shape) == (1, N):
+        if not (scale_a.is_contiguous() and scale_b.is_contiguous()):
+            reject("Both scale_a and scale_b must be contiguous for RowWise scaling.")
+        scaling = "rowwise"
+    else:
+        reject("Invalid scaling configuration. For TensorWise scaling, both scales should be scalar.")
+    if scale_result is not None and (scale_result.numel() != 1 or scale_result.dtype != torch.float32):
+        reject("scale_result must be a float scalar")
+    if bias is not None and bias.numel() != N:
+        reject(f"Bias must be size {N} but got {bias.numel()}")
+    if mat1.shape[1] % 16:
+        reject(f"Expected trailing dimension of mat1 to be divisible by 16 but got mat1 shape: "
+               f"({mat1.shape[0]}x{mat1.shape[1]}).")
+    if mat2.shape[0] % 16 or mat2.shape[1] % 16:
+        reject(f"mat2 shape ({mat2.shape[0]}x{mat2.shape[1]}) must be divisible by 16")
+    if out is not None and out_dtype is not None and out_dtype != out.dtype:
+        reject("out_dtype must match output matrix type")
+    od = out_dtype if out_dtype is not None else (out.dtype if out is not None else mat1.dtype)
+    for name, t in (("mat1", mat1), ("mat2", mat2)):
+        if t.dtype not in _TORCH_FLOAT8:
+            reject(f"Expected {name} to be Float8 matrix got {t.dtype}")
+    if mat1.dtype == E5M2 and mat2.dtype == E5M2:
+        reject("Multiplication of two Float8_e5m2 matrices is not supported")
+    if bias is not None:
+        if od == torch.float32:
+            reject("Bias is not supported when out_dtype is set to Float32")
+        if bias.dtype not in (torch.bfloat16, torch.float16):
+            reject(f"Bias must be either Half or BFloat16, but got {bias.dtype}")
+        if od in (torch.bfloat16, torch.float16) and bias.dtype != od:
+            reject(f"Bias must be {od} to compute {od} output, but got {bias.dtype}")
+    for t in (out, mat2, bias, scale_a, scale_b, scale_result):
+        if t is not None and t.device != mat1.device:
+            reject(f"Expected all tensors to be on the same device, but found at least two devices, {mat1.device} and "
+                   f"{t.device}!")
+    return scaling, od
+
+
+def _check_like_cublas(mat1, mat2, scaling, od):
+    """Checks that apply to non-empty calls only. Returns mat1 as cuBLAS reads it (torch copies a mat1 that is neither
+    row- nor column-major to a contiguous one)."""
+    def reject(msg):
+        raise ReferenceRejectsError(msg)
+    if scaling == "rowwise" and od != torch.bfloat16:
+        reject("Only bf16 high precision output types are supported for row-wise scaling.")
+    if _col_major(mat1) or not _row_major(mat2.t()):
+        reject("Only multiplication of row-major and column-major matrices is supported by cuBLASLt")
+    if not _row_major(mat1):
+        mat1 = mat1.contiguous()
+    for name, t in (("mat1", mat1), ("mat2", mat2)):
+        if not is_fp8_dtype(t.dtype):
+            reject(f"{name} is {t.dtype}: torch 2.7.1 fails on CUDA for FP8 formats other than float8_e4m3fn and "
+                   f"float8_e5m2")
+    if od not in OUT_DTYPE_NAMES:
+        reject(f"out dtype {od} is not supported by cuBLASLt FP8 GEMMs (CUBLAS_STATUS_NOT_SUPPORTED)")
+    if _misaligned(mat1) or _misaligned(mat2):
+        reject("CUBLAS_STATUS_NOT_SUPPORTED when calling cublasLtMatmul (operand pointer not 16-byte aligned)")
+    lda = mat1.stride(0) if mat1.shape[0] > 1 else mat1.shape[1]
+    ldb = mat2.stride(1) if mat2.shape[1] > 1 else mat2.shape[0]
+    if lda % 16 or ldb % 16:
+        reject("CUBLAS_STATUS_NOT_SUPPORTED when calling cublasLtMatmulAlgoGetHeuristic (leading dimension not a "
+               "multiple of 16)")
+    return mat1
+
+
+def _check_scope(scaling, bias, tensors):
+    if bias is not None:
+        raise UnsupportedFeatureError("bias is not supported (cuBLAS's fused-bias epilogue is not modelled); add the "
+                                      "bias yourself after scaled_mm")
+    if scaling == "rowwise":
+        raise UnsupportedFeatureError("row-wise scales are not supported (they run through a stream-K kernel whose "
+                                      "split depends on the SM count)")
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise UnsupportedFeatureError("inference only: an input requires grad while grad mode is enabled (use "
+                                      "torch.no_grad() or detach the inputs)")
+
+
+def _kernel_choice(backend: str) -> str:
+    """'auto' | 'integer' | 'fast' for a backend name; BackendUnavailableError for the reference's own backends."""
+    if not isinstance(backend, str):
+        raise TypeError(f"backend must be a str, got {type(backend).__name__}")
+    if backend == "auto":
+        backend = os.environ.get("MMAEMU_BACKEND", "").strip() or "auto"
+    if backend in _KERNEL_OF:
+        return _KERNEL_OF[backend]
+    if backend == "reference" or backend.startswith("cuda:"):
+        raise BackendUnavailableError(f"backend {backend!r} is not part of mmaemu_b200 (available: "
+                                      f"{', '.join(BACKEND_NAMES)}); the float64 reference model and the NVRTC kernels "
+                                      f"live in the mmaemu package")
+    raise ValueError(f"unknown backend {backend!r}; expected one of {', '.join(BACKEND_NAMES)}")
+
+
+def _require_device(device: torch.device) -> None:
+    if device.type != "cuda":
+        raise BackendUnavailableError(f"mmaemu_b200 runs on sm_100 CUDA devices only and has no CPU fallback; got "
+                                      f"tensors on {device}")
+    L = _lib.load()
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    _lib.check("mmb200_device_supported", L.mmb200_device_supported(idx))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+class _Call:
+    """A validated call: shapes, formats, profile, split decision, kernel choice."""
+    __slots__ = ("early", "unchanged_out", "M", "N", "K", "fa", "fb", "od", "profile", "preset", "decision", "scheme",
+                 "kernel", "mat1", "notes")
+
+
+def _emit_profile_warning(prof) -> None:
+    msg = profile_maturity_warning(prof)
+    if msg is not None and prof.name not in _warned_profiles:
+        _warned_profiles.add(prof.name)
+        warnings.warn(msg, ExperimentalPresetWarning, stacklevel=5)
+
+
+def _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out, profile, splitk,
+             backend, *, dry: bool) -> _Call:
+    c = _Call()
+    c.notes = []
+    _check_argument_types(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out)
+    scaling, c.od = _check_like_torch(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, out)
+    c.M, c.K, c.N = input.shape[0], input.shape[1], mat2.shape[1]
+    c.profile = get_profile(profile)
+    c.preset = get_preset(c.profile.preset)
+    c.early = c.M == 0 or c.N == 0 or c.K == 0
+    c.unchanged_out = False
+    c.decision = c.kernel = c.fa = c.fb = None
+    c.scheme = "none"
+    c.mat1 = input
+    if c.early:
+        return c
+    c.mat1 = _check_like_cublas(input, mat2, scaling, c.od)
+    c.fa, c.fb = fmt_of(c.mat1.dtype), fmt_of(mat2.dtype)
+    rule = c.profile.rejection(c.fa, c.fb, c.od)
+    if rule is not None:
+        raise ReferenceRejectsError(f"{rule.message} [profile {c.profile.name}]")
+    _check_scope(scaling, bias, (c.mat1, mat2, scale_a, scale_b, scale_result, bias))
+    msg = profile_maturity_warning(c.profile)
+    if msg is not None:
+        c.notes.append(msg)
+        if not dry:
+            _emit_profile_warning(c.profile)
+    same_shape = out is not None and tuple(out.shape) == (c.M, c.N)
+    if same_shape and not (_row_major(out) or _col_major(out)):
+        # torch computes into a contiguous copy of such an out= and never copies the result back
+        c.unchanged_out = True
+        c.notes.append(f"out= with strides {tuple(out.stride())} is neither row- nor column-major: torch 2.7.1 computes "
+                       f"into a contiguous copy and never copies it back, so out= is returned unchanged")
+        return c
+    layout_std = c.mat1.is_contiguous() and mat2.t().is_contiguous()
+    if same_shape and _col_major(out):
+        # a column-major out= is computed as the transposed problem with the formats swapped
+        key = (c.N, c.M, c.K, mat2.dtype, c.mat1.dtype)
+    else:
+        key = (c.M, c.N, c.K, c.mat1.dtype, mat2.dtype)
+    c.decision = resolve_splitk(key[0], key[1], key[2], a_dtype=key[3], b_dtype=key[4], out_dtype=c.od,
+                                use_fast_accum=bool(use_fast_accum), profile=c.profile, splitk=splitk,
+                                layout_std=layout_std, dry=dry)
+    c.kernel = _kernel_choice(backend)
+    if not dry:
+        _require_device(c.mat1.device)
+    return c
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _scalar_ptr(t: torch.Tensor, device) -> tuple:
+    """(keep-alive tensor, device pointer) of a one-element fp32 tensor on `device`."""
+    t = t.detach()
+    if t.device != device or not t.is_contiguous():
+        t = t.to(device).contiguous()
+    return t, t.data_ptr()
+
+
+def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -> torch.Tensor:
+    dev = c.mat1.device
+    a = c.mat1.detach()
+    bt = mat2.detach().t()                               # [N, K] with unit stride along K
+    lda = a.stride(0) if c.M > 1 else c.K
+    ldb = bt.stride(0) if c.N > 1 else c.K
+    y = torch.empty((c.M, c.N), dtype=c.od, device=dev)
+    keep_a, pa = _scalar_ptr(scale_a, dev)
+    keep_b, pb = _scalar_ptr(scale_b, dev)
+    keep_r, pr = (None, None) if scale_result is None else _scalar_ptr(scale_result, dev)
+    L = _lib.load()
+    with torch.cuda.device(dev):
+        rc = L.mmb200_scaled_mm(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb, _lib.FMT_CODES[c.fb],
+                                y.data_ptr(), c.N, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K, c.preset.nfma,
+                                int(fast), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb, pr,
+                                _lib.KERNEL_CODES[c.kernel], _stream_ptr(dev))
+    _lib.check("mmb200_scaled_mm", rc)
+    del keep_a, keep_b, keep_r
+    return y
+
+
+def scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_dtype=None, use_fast_accum=False,
+              *, out=None, profile=None, splitk="auto", backend="auto"):
+    """torch._scaled_mm with the numerics of the profile's GPU, computed by the B200 kernels.
+
+    input [M, K] FP8 row-major; mat2 [K, N] FP8 column-major (e.g. w.t() of a row-major [N, K] weight); scale_a,
+    scale_b: one-element fp32 tensors. Returns [M, N] of out_dtype (default input.dtype) on input.device, which must
+    be an sm_100 CUDA device. profile: one of hopper (default, or $MMAEMU_PROFILE), hopper-te, hopper-ws0, ada,
+    ada-te, ada-ws0. splitk: "auto", 1, a SplitK or (S, scheme). backend: "auto" | "cuda" | "cuda:b200" |
+    "cuda:b200-integer" | "cuda:b200-fast". Raises what the reference raises (module docstring)."""
+    c = _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out, profile, splitk,
+                 backend, dry=False)
+    if c.unchanged_out:
+        warnings.warn(c.notes[-1], UserWarning, stacklevel=2)
+        return out
+    if c.early:
+        y = torch.zeros(c.M, c.N, dtype=c.od, device=input.device)
+    else:
+        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+        y = _run_scaled_mm(c, mat2, scale_a, scale_b, scale_result, bool(use_fast_accum))
+    if out is None:
+        return y
+    if tuple(out.shape) != (c.M, c.N):
+        if out.numel() != 0:
+            warnings.warn(f"An output with one or more elements was resized since it had shape {list(out.shape)}, "
+                          f"which does not match the required output shape {[c.M, c.N]}.", UserWarning, stacklevel=2)
+        out.resize_(c.M, c.N)
+    out.copy_(y)
+    return out
+
+
+def accumulate(a, b, *, use_fast_accum, profile=None, splitk="auto", backend="auto",
+               out_dtype_for_split=torch.float32):
+    """fp32 [M, N] accumulator of a [M, K] x b [N, K]^T before alpha, as the profile's cuBLAS computes it (the
+    reference's mmaemu.accumulate, mmaemu/api.py:382-421). a, b: FP8 tensors of any K, alignment or layout.
+    use_fast_accum has no default on purpose. The split decision is keyed with out_dtype_for_split."""
+    for name, v in (("a", a), ("b", b)):
+        if not isinstance(v, torch.Tensor):
+            raise TypeError(f"accumulate(): argument '{name}' must be Tensor, not {type(v).__name__}")
+    if not isinstance(use_fast_accum, bool) and type(use_fast_accum).__name__ != "bool_":
+        raise TypeError(f"accumulate(): use_fast_accum must be bool, not {type(use_fast_accum).__name__}")
+    if not isinstance(out_dtype_for_split, torch.dtype):
+        raise TypeError("accumulate(): out_dtype_for_split must be a torch.dtype")
+    fa, fb = fmt_of(a.dtype), fmt_of(b.dtype)
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError(f"accumulate(): expected a [M, K] and b [N, K], got {tuple(a.shape)} and {tuple(b.shape)}")
+    if a.shape[1] != b.shape[1]:
+        raise ValueError(f"accumulate(): K mismatch: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if a.device != b.device:
+        raise ValueError(f"accumulate(): a and b are on different devices ({a.device}, {b.device})")
+    if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad):
+        raise UnsupportedFeatureError("inference only: an input requires grad while grad mode is enabled")
+    prof = get_profile(profile)
+    preset = get_preset(prof.preset)
+    _emit_profile_warning(prof)
+    M, K, N = a.shape[0], a.shape[1], b.shape[0]
+    fast = bool(use_fast_accum)
+    if M == 0 or N == 0 or K == 0:
+        return torch.zeros(M, N, dtype=torch.float32, device=a.device)
+    decision = resolve_splitk(M, N, K, a_dtype=a.dtype, b_dtype=b.dtype, out_dtype=out_dtype_for_split,
+                              use_fast_accum=fast, profile=prof, splitk=splitk, layout_std=True)
+    kernel = _kernel_choice(backend)
+    _require_device(a.device)
+    scheme = check_plan(preset, K, decision.S, decision.scheme)
+    dev = a.device
+    au, bu = a.detach().contiguous(), b.detach().contiguous()
+    acc = torch.empty((M, N), dtype=torch.float32, device=dev)
+    L = _lib.load()
+    with torch.cuda.device(dev):
+        rc = L.mmb200_accumulate(au.data_ptr(), K, _lib.FMT_CODES[fa], bu.data_ptr(), K, _lib.FMT_CODES[fb],
+                                 acc.data_ptr(), N, M, N, K, preset.nfma, int(fast), decision.S,
+                                 _lib.SCHEME_CODES[scheme], _lib.KERNEL_CODES[kernel], _stream_ptr(dev))
+    _lib.check("mmb200_accumulate", rc)
+    return acc
+
+
+def explain(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_dtype=None, use_fast_accum=False,
+            *, out=None, profile=None, splitk="auto", backend="auto") -> CallPlan:
+    """Validate a scaled_mm call and report what it would do, without computing (same arguments as scaled_mm)."""
+    cp = CallPlan()
+    try:
+        with warnings.catch_warnings(record=True) as seen:
+            warnings.simplefilter("always")
+            c = _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out, profile,
+                         splitk, backend, dry=True)
+            if not (c.early or c.unchanged_out):
+                check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+        cp.warnings = list(c.notes) + [str(w.message) for w in seen]
+        cp.profile, cp.preset, cp.preset_maturity = c.profile.name, c.preset.name, c.preset.maturity
+        cp.split = c.decision
+        if c.early:
+            cp.backend = "none (zero-size result)"
+        elif c.unchanged_out:
+            cp.backend = "none (out= is returned unchanged)"
+        else:
+            cp.backend = "cuda:b200" if c.kernel == "auto" else f"cuda:b200-{c.kernel}"
+    except Exception as e:  # noqa: BLE001 - explain reports instead of raising
+        cp.validation = (type(e).__name__, str(e))
+        try:
+            prof = get_profile(profile)
+            preset = get_preset(prof.preset)
+            cp.profile, cp.preset, cp.preset_maturity = prof.name, preset.name, preset.maturity
+        except Exception:  # noqa: BLE001
+            pass
+    return cp
+
+
+# torch.compile must not trace into these entry points (they call a foreign library through ctypes)
+scaled_mm = torch.compiler.disable(scaled_mm)
+accumulate = torch.compiler.disable(accumulate)
+explain = torch.compiler.disable(explain)

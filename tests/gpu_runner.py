@@ -1,0 +1,79 @@
+"""Runs numpy operands through the C ABI of libmmaemu_b200.so on cuda:0 and returns output bits (GPU tests only).
+
+`scaled_mm` and `accumulate` take the same keyword arguments as the oracle's functions, so a test can feed one case to
+both and compare. torch is used for device memory and the stream only."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from mmaemu_b200 import _lib
+
+OUT_NP = {"float32": np.uint32, "bfloat16": np.uint16, "float16": np.uint16, "float8_e4m3fn": np.uint8,
+          "float8_e5m2": np.uint8}
+OUT_TORCH = {"float32": torch.int32, "bfloat16": torch.int16, "float16": torch.int16, "float8_e4m3fn": torch.uint8,
+             "float8_e5m2": torch.uint8}
+DEV = torch.device("cuda:0")
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+
+
+def _dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def scaled_mm(a, b, scale_a, scale_b, *, out="bfloat16", fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=False, S=1,
+              scheme="none", scale_result=None, kernel="auto", ld_pad=0):
+    L = _lib.load()
+    M, K = a.shape
+    N = b.shape[0]
+    if ld_pad:                                   # operands with a leading dimension larger than K
+        a = np.concatenate([a, np.full((M, ld_pad), 0x55, np.uint8)], axis=1)
+        b = np.concatenate([b, np.full((N, ld_pad), 0xAA, np.uint8)], axis=1)
+    A, B = _dev(a), _dev(b)
+    D = torch.full((M, max(N, 1)), -1 if OUT_TORCH[out] != torch.uint8 else 0xEE, dtype=OUT_TORCH[out], device=DEV)
+    sc = torch.tensor([scale_a, scale_b, 1.0 if scale_result is None else scale_result], dtype=torch.float32,
+                      device=DEV)
+    rc = L.mmb200_scaled_mm(A.data_ptr(), K + ld_pad, _lib.FMT_CODES[fmt_a], B.data_ptr(), K + ld_pad,
+                            _lib.FMT_CODES[fmt_b], D.data_ptr(), max(N, 1), _lib.OUT_CODES[out], M, N, K, int(preset),
+                            int(bool(fast)), int(S), _lib.SCHEME_CODES[scheme], sc.data_ptr(), sc.data_ptr() + 4,
+                            None if scale_result is None else sc.data_ptr() + 8, _lib.KERNEL_CODES[kernel], _stream())
+    _lib.check("mmb200_scaled_mm", rc)
+    torch.cuda.synchronize(DEV)
+    return D[:, :N].cpu().numpy().view(OUT_NP[out])
+
+
+def accumulate(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=True, S=1, scheme="none", kernel="auto"):
+    L = _lib.load()
+    M, K = a.shape
+    N = b.shape[0]
+    A, B = _dev(a), _dev(b)
+    C = torch.full((M, max(N, 1)), -1, dtype=torch.int32, device=DEV)
+    rc = L.mmb200_accumulate(A.data_ptr(), max(K, 1), _lib.FMT_CODES[fmt_a], B.data_ptr(), max(K, 1),
+                             _lib.FMT_CODES[fmt_b], C.data_ptr(), max(N, 1), M, N, K, int(preset), int(bool(fast)),
+                             int(S), _lib.SCHEME_CODES[scheme], _lib.KERNEL_CODES[kernel], _stream())
+    _lib.check("mmb200_accumulate", rc)
+    torch.cuda.synchronize(DEV)
+    return C[:, :N].cpu().numpy().view(np.uint32)
+
+
+def chain(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, kernel="auto"):
+    L = _lib.load()
+    M, K = a.shape
+    N = b.shape[0]
+    A, B = _dev(a), _dev(b)
+    C = torch.full((M, N), -1, dtype=torch.int32, device=DEV)
+    rc = L.mmb200_chain(A.data_ptr(), K, _lib.FMT_CODES[fmt_a], B.data_ptr(), K, _lib.FMT_CODES[fmt_b], C.data_ptr(),
+                        N, M, N, K, int(preset), _lib.KERNEL_CODES[kernel], _stream())
+    _lib.check("mmb200_chain", rc)
+    torch.cuda.synchronize(DEV)
+    return C.cpu().numpy().view(np.uint32)
+
+
+def for_kernel(kernel):
+    """(scaled_mm, accumulate) bound to one kernel family."""
+    return (lambda *a, **k: scaled_mm(*a, kernel=kernel, **k)), (lambda *a, **k: accumulate(*a, kernel=kernel, **k))

@@ -1,0 +1,66 @@
+"""The C-ABI library loads on a machine without a GPU and exports every function include/mmaemu_b200.h declares; calls
+that need a device fail with a status, never with a crash. No kernel is launched here."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = (ROOT / "include" / "mmaemu_b200.h").read_text()
+
+
+def declared_functions():
+    code = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+    return sorted(set(re.findall(r"\b(mmb200_[a-z0-9_]+)\s*\(", code)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as entry
+    entry.build()
+    from mmaemu_b200 import _lib
+    return _lib.load()
+
+
+def test_header_declares_the_expected_entry_points():
+    from mmaemu_b200 import _lib
+    assert set(declared_functions()) == set(_lib.EXPORTS)
+
+
+def test_every_declared_function_is_exported(lib):
+    for name in declared_functions():
+        assert hasattr(lib, name), name
+
+
+def test_status_codes_and_argument_checks_without_a_device(lib):
+    from mmaemu_b200 import _lib
+    assert lib.mmb200_abi_version() == int(re.search(r"#define MMB200_ABI_VERSION (\d+)", HEADER).group(1))
+    for code in (0, -1, -2, -3, -4, -5):
+        assert lib.mmb200_status_string(code).decode() not in ("", "unknown status")
+    assert lib.mmb200_status_string(-99).decode() == "unknown status"
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    # argument errors are reported before any CUDA call
+    assert lib.mmb200_chain(p, 16, 7, p, 16, 0, p, 1, 1, 1, 16, 32, 0, None) == _lib.ERR_BAD_ARG      # bad format
+    assert lib.mmb200_chain(p, 8, 0, p, 16, 0, p, 1, 1, 1, 16, 32, 0, None) == _lib.ERR_BAD_ARG       # lda < K
+    assert lib.mmb200_chain(p, 16, 0, p, 16, 0, p, 1, 1, 1, 16, 24, 0, None) == _lib.ERR_UNSUPPORTED  # nfma
+    assert lib.mmb200_accumulate(p, 16, 0, p, 16, 0, p, 1, 1, 1, 16, 32, 1, 2, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert lib.mmb200_accumulate(p, 16, 0, p, 16, 0, p, 1, 1, 1, 16, 32, 1, 65, 3, 0, None) == _lib.ERR_TOO_LARGE
+    assert lib.mmb200_scaled_mm(p, 16, 0, p, 16, 0, p, 1, 1, 1, 1, 16, 32, 1, 1, 0, None, None, None, 0, None) \
+        == _lib.ERR_BAD_ARG                                                                            # no scales
+    assert lib.mmb200_chain(p, 16, 0, p, 16, 0, p, 1, 0, 5, 16, 32, 0, None) == _lib.OK               # empty result
+    assert lib.mmb200_launch_count() == 0
+
+
+def test_no_device_is_a_status_not_a_crash(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    from mmaemu_b200 import _lib
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    rc = lib.mmb200_chain(p, 16, 0, p, 16, 0, p, 1, 1, 1, 16, 32, 0, None)
+    assert rc in (_lib.ERR_LAUNCH, _lib.ERR_ARCH)
+    with pytest.raises(Exception):
+        _lib.check("mmb200_chain", rc)

@@ -1,0 +1,167 @@
+"""The Python entry points on a B200 (-m gpu): mmaemu_b200.scaled_mm / accumulate / the Backend object, bit for bit
+against the oracle, plus the behaviours the reference pins at this boundary (tests/test_api.py and
+tests/test_cuda_runtime.py of astding/mmaemu): out= handling, zero sizes, storage offsets, the current stream."""
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+import datagen
+import mmaemu_b200 as mm
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+F8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+NPV = {4: (torch.int32, np.uint32), 2: (torch.int16, np.uint16), 1: (torch.uint8, np.uint8)}
+
+
+def bits(t):
+    tv, nv = NPV[t.element_size()]
+    return t.detach().cpu().contiguous().view(tv).numpy().view(nv)
+
+
+def operands(M, N, K, fa="e4m3", fb="e4m3", seed=0, scale=4.0):
+    rng = np.random.default_rng(seed)
+    a = datagen._round_to(rng.standard_normal((M, K)) * scale, fa)
+    b = datagen._round_to(rng.standard_normal((N, K)) * scale, fb)
+    return a, b, torch.from_numpy(a).to(DEV).view(F8[fa]), torch.from_numpy(b).to(DEV).view(F8[fb])
+
+
+@pytest.mark.parametrize("profile", ("hopper", "hopper-te", "hopper-ws0", "ada", "ada-te", "ada-ws0"))
+@pytest.mark.parametrize("fast", (True, False))
+def test_scaled_mm_profiles(profile, fast):
+    a, b, ta, tb = operands(64, 128, 1024, seed=1)
+    sa, sb = torch.tensor(0.5, device=DEV), torch.tensor(1.25, device=DEV)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        y = mm.scaled_mm(ta, tb.t(), sa, sb, out_dtype=torch.bfloat16, use_fast_accum=fast, profile=profile, splitk=1)
+    want = oracle.scaled_mm(a, b, 0.5, 1.25, out="bfloat16", preset=profile.split("-")[0], fast=fast)
+    assert y.dtype == torch.bfloat16 and y.device == DEV and np.array_equal(bits(y), want)
+
+
+def test_config1_ada_256_cube():
+    """M = N = K = 256, profile 'ada', seeds 0 / 1, scales 0.5 and 1.25, bf16 out, split-K from the table."""
+    A = (torch.randn(256, 256, generator=torch.Generator().manual_seed(0)) * 2).to(torch.float8_e4m3fn)
+    Bt = torch.randn(256, 256, generator=torch.Generator().manual_seed(1)).to(torch.float8_e4m3fn)
+    for fast in (False, True):
+        y = mm.scaled_mm(A.to(DEV), Bt.to(DEV).t(), torch.tensor(0.5, device=DEV), torch.tensor(1.25, device=DEV),
+                         out_dtype=torch.bfloat16, use_fast_accum=fast, profile="ada")
+        want = oracle.scaled_mm(A.view(torch.uint8).numpy(), Bt.view(torch.uint8).numpy(), 0.5, 1.25, out="bfloat16",
+                                preset="ada", fast=fast)
+        assert np.array_equal(bits(y), want)
+    with pytest.raises(mm.SplitKUnknownError):
+        mm.scaled_mm(A.to(DEV), Bt.to(DEV).t(), torch.tensor(0.5, device=DEV), torch.tensor(1.25, device=DEV),
+                     out_dtype=torch.bfloat16, profile="hopper")
+
+
+def _h100_jobs():
+    import json
+    import golden_cases as G
+    return [j for j in json.loads((G.GOLDEN / "h100_mini.json").read_text())["jobs"]]
+
+
+@pytest.mark.parametrize("j", _h100_jobs(), ids=lambda j: j["id"])
+def test_h100_live_calls_through_scaled_mm(j):
+    """The recorded H100 PCIe calls through the public entry point: the logged split passed explicitly must give the
+    H100's output bits (sha256), the two calls the H100 rejected must raise, and splitk='auto' must resolve to the
+    logged split wherever the profile's table holds the shape."""
+    import hashlib
+    import h100_inputs
+    a, b = h100_inputs.make_inputs(j)
+    ta = torch.from_numpy(a).to(DEV).view(F8[j["fa"]])
+    tb = torch.from_numpy(b).to(DEV).view(F8[j["fb"]])
+    sa, sb = torch.tensor(j["scale_a"], device=DEV), torch.tensor(j["scale_b"], device=DEV)
+    sr = None if j["scale_result"] is None else torch.tensor(j["scale_result"], device=DEV)
+    profile = {0: "hopper-ws0", 1 << 20: "hopper", 32 << 20: "hopper-te"}.get(j["ws"])
+    kw = dict(scale_result=sr, out_dtype=getattr(torch, j["out"]), use_fast_accum=bool(j["fast"]),
+              profile=profile or "hopper")
+    if "error" in j["expect"]:
+        with pytest.raises(getattr(mm, j["expect"]["error"])) as ei:
+            mm.scaled_mm(ta, tb.t(), sa, sb, splitk=1, **kw)
+        assert type(ei.value) is getattr(mm, j["expect"]["error"])
+        return
+    split = 1 if j["S"] == 1 else (j["S"], j["scheme"])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        y = mm.scaled_mm(ta, tb.t(), sa, sb, splitk=split, **kw)
+        cp = mm.explain(ta, tb.t(), sa, sb, splitk="auto", **kw)
+    assert hashlib.sha256(bits(y).tobytes()).hexdigest() == j["expect"]["sha256"]
+    if profile is not None and (j["src"] == "m6_live" or cp.validation == "ok"):
+        assert cp.validation == "ok", cp.validation
+        assert (cp.split.S, cp.split.scheme) == (j["S"], j["scheme"] if j["S"] > 1 else "none")
+
+
+def test_out_argument_zero_sizes_and_offsets():
+    a, b, ta, tb = operands(32, 48, 256, seed=4)
+    s = torch.tensor(1.0, device=DEV)
+    kw = dict(out_dtype=torch.float32, profile="ada", splitk=1)
+    y = mm.scaled_mm(ta, tb.t(), s, s, **kw)
+    out = torch.full((32, 48), 7.0, device=DEV)
+    assert mm.scaled_mm(ta, tb.t(), s, s, out=out, **kw) is out and torch.equal(out, y)
+    colmajor = torch.full((48, 32), 7.0, device=DEV).t()
+    mm.scaled_mm(ta, tb.t(), s, s, out=colmajor, **kw)
+    assert torch.equal(colmajor, y)
+    with pytest.warns(UserWarning, match="resized"):
+        wrong = torch.zeros(3, 5, device=DEV)
+        mm.scaled_mm(ta, tb.t(), s, s, out=wrong, **kw)
+    assert torch.equal(wrong, y)
+    strided = torch.full((32, 96), 7.0, device=DEV)[:, ::2]
+    with pytest.warns(UserWarning, match="unchanged"):
+        r = mm.scaled_mm(ta, tb.t(), s, s, out=strided, **kw)
+    assert r is strided and bool((strided == 7.0).all())
+    z = mm.scaled_mm(ta[:, :0], tb[:, :0].t(), s, s, **kw)
+    assert z.shape == (32, 48) and not bool(z.any())
+    assert mm.scaled_mm(ta[:0], tb.t(), s, s, **kw).shape == (0, 48)
+    # operands that are views into larger buffers (16-byte aligned offsets, padded leading dimension)
+    big = torch.zeros(32 * 272 + 64, dtype=torch.uint8, device=DEV)
+    va = big[32:32 + 32 * 272].view(32, 272)[:, :256]
+    va.copy_(ta.view(torch.uint8))
+    y2 = mm.scaled_mm(va.view(torch.float8_e4m3fn), tb.t(), s, s, **kw)
+    assert torch.equal(y2, y)
+    with pytest.raises(mm.ReferenceRejectsError):
+        mm.scaled_mm(big[8:8 + 32 * 256].view(32, 256).view(torch.float8_e4m3fn), tb.t(), s, s, **kw)
+
+
+def test_runs_on_the_current_stream():
+    a, b, ta, tb = operands(256, 256, 2048, seed=5)
+    s = torch.tensor(1.0, device=DEV)
+    st = torch.cuda.Stream(DEV)
+    with torch.cuda.stream(st):
+        y = mm.scaled_mm(ta, tb.t(), s, s, out_dtype=torch.float32, profile="ada", splitk=1, use_fast_accum=True)
+    st.synchronize()
+    assert np.array_equal(bits(y), oracle.accumulate(a, b, preset="ada", fast=True))
+
+
+def test_accumulate_any_k():
+    for K in (8, 24, 200):
+        a, b, ta, tb = operands(20, 31, K, "e4m3", "e5m2", seed=K)
+        acc = mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
+        assert np.array_equal(bits(acc), oracle.accumulate(a, b, fmt_a="e4m3", fmt_b="e5m2", preset="ada", fast=False))
+
+
+def test_backend_object_chain_fn():
+    from types import SimpleNamespace
+    from mmaemu_b200.backend import BACKEND
+    req = SimpleNamespace(device=DEV, fmt_a="e5m2", fmt_b="e4m3", preset="hopper")
+    assert BACKEND.supports(req) is None
+    fn = BACKEND.chain_fn(req)
+    a, b, ta, tb = operands(65, 63, 48, "e5m2", "e4m3", seed=6)
+    got = fn(ta.view(torch.uint8)[1:], tb)                      # a view with a storage offset
+    assert np.array_equal(bits(got), oracle.accumulate(a[1:], b, fmt_a="e5m2", fmt_b="e4m3", preset="hopper", fast=True))
+    with pytest.raises(ValueError):
+        fn(ta.view(torch.uint8)[:, :40], tb.view(torch.uint8)[:, :40])
+    with pytest.raises(TypeError):
+        fn(ta.view(torch.uint8).float(), tb)
+    with pytest.raises(ValueError):
+        fn(ta.view(torch.uint8).cpu(), tb)
+    assert BACKEND.supports(SimpleNamespace(device="cpu", fmt_a="e4m3", fmt_b="e4m3", preset="ada")) is not None
+
+
+def test_launch_accounting():
+    from mmaemu_b200 import _lib
+    a, b, ta, tb = operands(16, 16, 64, seed=7)
+    n0 = _lib.launch_count()
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
+    assert _lib.launch_count() == n0 + 1

@@ -1,0 +1,194 @@
+"""Host-side behaviour of mmaemu_b200.scaled_mm / accumulate / explain on CPU tensors (no GPU, no kernel launch):
+the signature, every rejection with its exact exception class, the validation order, zero-size results, split-K
+resolution and the backend names -- the contract of the reference's tests/test_api.py for this path."""
+import inspect
+import warnings
+
+import pytest
+import torch
+
+import mmaemu_b200 as mm
+from mmaemu_b200 import api
+
+E4, E5 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+def ops(M=32, N=48, K=64, da=E4, db=E4):
+    a = torch.zeros(M, K).to(da)
+    b = torch.zeros(N, K).to(db)
+    return a, b.t(), torch.tensor(1.0), torch.tensor(1.0)
+
+
+def raises_exactly(cls, *args, **kw):
+    with pytest.raises(cls) as ei:
+        mm.scaled_mm(*args, **kw)
+    assert type(ei.value) is cls, type(ei.value)
+    return ei.value
+
+
+def test_signature_is_torch_scaled_mm_plus_keywords():
+    sig = inspect.signature(mm.scaled_mm)
+    names = list(sig.parameters)
+    assert names == ["input", "mat2", "scale_a", "scale_b", "bias", "scale_result", "out_dtype", "use_fast_accum", "out",
+                     "profile", "splitk", "backend"]
+    p = sig.parameters
+    assert p["use_fast_accum"].default is False and p["out_dtype"].default is None and p["bias"].default is None
+    assert p["splitk"].default == "auto" and p["backend"].default == "auto" and p["profile"].default is None
+    assert all(p[n].kind is inspect.Parameter.KEYWORD_ONLY for n in ("out", "profile", "splitk", "backend"))
+    assert inspect.signature(mm.explain).parameters.keys() == sig.parameters.keys()
+    acc = inspect.signature(mm.accumulate).parameters
+    assert acc["use_fast_accum"].default is inspect.Parameter.empty
+
+
+def test_argument_types():
+    a, bt, s, _ = ops()
+    raises_exactly(TypeError, a.float().numpy(), bt, s, s)
+    raises_exactly(TypeError, a, bt, 1.0, s)
+    raises_exactly(TypeError, a, bt, s, s, bias=1.0)
+    raises_exactly(TypeError, a, bt, s, s, out_dtype="bfloat16")
+    raises_exactly(TypeError, a, bt, s, s, use_fast_accum=1)
+    raises_exactly(TypeError, a, bt, s, s, out=3)
+
+
+@pytest.mark.parametrize("make,kw", [
+    (lambda: (torch.zeros(32).to(E4), ops()[1]), {}),
+    (lambda: (ops()[0], torch.zeros(48, 48).to(E4).t()), {}),                            # inner dimensions differ
+    (lambda: (ops()[0].float(), ops()[1]), {}),                                          # not float8
+    (lambda: (ops(da=E5)[0], ops(db=E5)[1]), {}),                                        # e5m2 x e5m2
+    (lambda: (ops(K=72)[0], ops(K=72)[1]), {}),                                          # K % 16
+    (lambda: (ops()[0], ops(N=40)[1]), {}),                                              # N % 16
+    (lambda: ops()[:2], dict(out_dtype=torch.float32, out=torch.zeros(32, 48, dtype=torch.bfloat16))),
+    (lambda: ops()[:2], dict(scale_result=torch.tensor([1.0, 2.0]))),
+    (lambda: ops()[:2], dict(bias=torch.zeros(7, dtype=torch.bfloat16), out_dtype=torch.bfloat16)),
+    (lambda: ops()[:2], dict(bias=torch.zeros(48, dtype=torch.bfloat16), out_dtype=torch.float32)),
+    (lambda: ops()[:2], dict(out_dtype=torch.float64)),
+    (lambda: ops()[:2], dict(out_dtype=E5)),                                             # profile reject e4m3^2 -> e5m2
+    (lambda: (ops()[0].t().contiguous().t(), ops()[1]), {}),                             # column-major mat1
+    (lambda: (ops()[0], torch.zeros(64, 48).to(E4)), {}),                                # row-major mat2
+])
+def test_reference_rejects(make, kw):
+    a, bt = make()
+    kw.setdefault("out_dtype", torch.bfloat16)
+    raises_exactly(mm.ReferenceRejectsError, a, bt, torch.tensor(1.0), torch.tensor(1.0), profile="ada", **kw)
+
+
+def test_scale_checks():
+    a, bt, s, _ = ops()
+    raises_exactly(mm.ReferenceRejectsError, a, bt, s.double(), s, out_dtype=torch.bfloat16)
+    raises_exactly(mm.ReferenceRejectsError, a, bt, torch.ones(32), torch.ones(48), out_dtype=torch.bfloat16)
+    raises_exactly(mm.ReferenceRejectsError, a, bt, torch.ones(32, 2), torch.ones(2, 48), out_dtype=torch.bfloat16)
+    raises_exactly(mm.ReferenceRejectsError, a, bt, torch.ones(32, 1), torch.ones(1, 48), out_dtype=torch.float16)
+
+
+def test_scope_raises_unsupported_feature():
+    a, bt, s, _ = ops()
+    kw = dict(out_dtype=torch.bfloat16, profile="ada")
+    raises_exactly(mm.UnsupportedFeatureError, a, bt, s, s, torch.zeros(48, dtype=torch.bfloat16), **kw)   # positional
+    raises_exactly(mm.UnsupportedFeatureError, a, bt, s, s, bias=torch.zeros(48, dtype=torch.bfloat16), **kw)
+    raises_exactly(mm.UnsupportedFeatureError, a, bt, torch.ones(32, 1), torch.ones(1, 48), **kw)
+    sg = torch.tensor(1.0, requires_grad=True)
+    raises_exactly(mm.UnsupportedFeatureError, a, bt, sg, s, **kw)
+    with torch.no_grad():
+        raises_exactly(mm.BackendUnavailableError, a, bt, sg, s, **kw)          # valid: only the device is missing
+
+
+def test_validation_order():
+    a, bt, s, _ = ops()
+    bias = torch.zeros(48, dtype=torch.bfloat16)
+    # a torch-level rejection wins over the scope error, the scope error over split-K, split-K over the backend
+    raises_exactly(mm.ReferenceRejectsError, a, bt, s, s, bias=bias, out_dtype=torch.float32, profile="ada")
+    raises_exactly(mm.UnsupportedFeatureError, a, bt, s, s, bias=bias, out_dtype=torch.bfloat16, profile="hopper")
+    raises_exactly(mm.SplitKUnknownError, a, bt, s, s, out_dtype=torch.bfloat16, profile="hopper")
+    raises_exactly(mm.BackendUnavailableError, a, bt, s, s, out_dtype=torch.bfloat16, profile="hopper", splitk=1)
+    raises_exactly(ValueError, a, bt, s, s, out_dtype=torch.bfloat16, profile="ada", splitk=3)
+    raises_exactly(ValueError, a, bt, s, s, out_dtype=torch.bfloat16, profile="ada", backend="nope")
+    raises_exactly(mm.BackendUnavailableError, a, bt, s, s, out_dtype=torch.bfloat16, profile="ada", backend="cuda:h4")
+    raises_exactly(mm.BackendUnavailableError, a, bt, s, s, out_dtype=torch.bfloat16, profile="ada", backend="reference")
+
+
+def test_zero_sizes_return_before_the_cublas_checks():
+    s = torch.tensor(1.0)
+    for M, N, K in ((0, 48, 64), (32, 0, 64), (32, 48, 0)):
+        a, bt, _, _ = ops(M, N, K)
+        for od in (torch.float32, torch.bfloat16, E5):
+            y = mm.scaled_mm(a, bt, s, s, out_dtype=od)
+            assert y.shape == (M, N) and y.dtype == od and not bool(y.float().any())
+    fn = getattr(torch, "float8_e4m3fnuz", None)
+    if fn is not None:                                                     # accepted by torch before its early return
+        assert mm.scaled_mm(torch.zeros(0, 64).to(fn), torch.zeros(48, 64).to(fn).t(), s, s).shape == (0, 48)
+    assert mm.accumulate(torch.zeros(0, 8).to(E4), torch.zeros(3, 8).to(E4), use_fast_accum=True).shape == (0, 3)
+
+
+def test_explain_reports_instead_of_raising():
+    a, bt, s, _ = ops()
+    cp = mm.explain(a, bt, s, s, out_dtype=torch.bfloat16, profile="ada")
+    assert cp.validation == "ok" and (cp.profile, cp.preset, cp.preset_maturity) == ("ada", "ada", "validated")
+    assert (cp.split.S, cp.split.source) == (1, "table") and cp.backend == "cuda:b200"
+    cp = mm.explain(a, bt, s, s, out_dtype=torch.bfloat16)
+    assert cp.validation[0] == "SplitKUnknownError" and cp.profile == "hopper"
+    cp = mm.explain(a, bt, s, s, out_dtype=torch.bfloat16, profile="ada", splitk=(2, "contiguous"))
+    assert cp.validation[0] == "ValueError"
+    cp = mm.explain(a, bt, s, s, out_dtype=torch.bfloat16, profile="hopper", splitk=(2, "contiguous"),
+                    backend="cuda:b200-integer")
+    assert cp.validation == "ok" and cp.backend == "cuda:b200-integer" and cp.warnings
+    assert mm.explain(a[:, :0], bt[:0], s, s).backend.startswith("none")
+
+
+def test_column_major_out_swaps_the_split_key(monkeypatch):
+    seen = {}
+
+    def fake(M, N, K, **kw):
+        seen.update(M=M, N=N, a=kw["a_dtype"], b=kw["b_dtype"])
+        raise mm.SplitKUnknownError("stop")
+    monkeypatch.setattr(api, "resolve_splitk", fake)
+    a, bt, s, _ = ops(32, 48, 64, E4, E5)
+    with pytest.raises(mm.SplitKUnknownError):
+        mm.scaled_mm(a, bt, s, s, out=torch.zeros(48, 32).t(), profile="ada")
+    assert seen == dict(M=48, N=32, a=E5, b=E4)
+    with pytest.raises(mm.SplitKUnknownError):
+        mm.scaled_mm(a, bt, s, s, out=torch.zeros(32, 48), profile="ada")
+    assert seen == dict(M=32, N=48, a=E4, b=E5)
+
+
+def test_profiles_and_env(monkeypatch):
+    assert mm.list_profiles()[:6] == ["ada", "ada-te", "ada-ws0", "hopper", "hopper-te", "hopper-ws0"]
+    assert mm.get_profile().name == "hopper"
+    monkeypatch.setenv("MMAEMU_PROFILE", "ada-te")
+    assert mm.get_profile().name == "ada-te" and mm.get_profile().workspace_bytes == 4 << 20
+    with pytest.raises(KeyError):
+        mm.get_profile("h100")
+    a, bt, s, _ = ops()
+    with pytest.warns(mm.ExperimentalPresetWarning):
+        with pytest.raises(mm.SplitKUnknownError):
+            mm.scaled_mm(a, bt, s, s, out_dtype=torch.bfloat16, profile="hopper-experimental")
+    monkeypatch.setenv("MMAEMU_BACKEND", "cuda:v4")
+    with pytest.raises(mm.BackendUnavailableError):
+        mm.scaled_mm(a, bt, s, s, out_dtype=torch.bfloat16, profile="ada")
+
+
+def test_accumulate_argument_checks():
+    a, b = torch.zeros(4, 16).to(E4), torch.zeros(5, 16).to(E4)
+    with pytest.raises(TypeError):
+        mm.accumulate(a, b)                                                   # use_fast_accum has no default
+    with pytest.raises(TypeError):
+        mm.accumulate(a, b, use_fast_accum=1)
+    with pytest.raises(TypeError):
+        mm.accumulate(a.float(), b, use_fast_accum=True)
+    with pytest.raises(ValueError):
+        mm.accumulate(a, b[:, :8], use_fast_accum=True)
+    with pytest.raises(mm.BackendUnavailableError):
+        mm.accumulate(a, b, use_fast_accum=True, profile="ada", splitk=1)
+
+
+def test_presets():
+    from mmaemu_b200.numerics import check_plan, get_preset
+    assert (get_preset("ada").nfma, get_preset("hopper").nfma) == (16, 32)
+    with pytest.raises(mm.UnsupportedFeatureError):
+        get_preset("b200_mma_sync")
+    with pytest.raises(KeyError):
+        get_preset("volta")
+    assert check_plan(get_preset("ada"), 64, 1, "pairwise") == "none"
+    assert check_plan(get_preset("hopper"), 64, 4, "contiguous") == "contiguous"
+    for bad in ((get_preset("ada"), 4, "contiguous"), (get_preset("hopper"), 2, "serial"), (get_preset("ada"), 2, "x")):
+        with pytest.raises(ValueError):
+            check_plan(bad[0], 64, bad[1], bad[2])
