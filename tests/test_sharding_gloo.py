@@ -1,0 +1,114 @@
+"""The multi-GPU sharding logic on two CPU ranks (gloo): row partition, split-K decided on the full shape, all-gather
+of equal and ragged slabs. The per-rank compute is a stand-in that calls the CPU oracle, so the assembled result must
+equal the oracle on the whole problem bit for bit."""
+import os
+import socket
+import warnings
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from mmaemu_b200.sharding import shard_rows
+
+F8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+
+
+def test_shard_rows_cover_every_row_once():
+    for M in (0, 1, 127, 128, 129, 1000, 4096, 32768):
+        for world in (1, 2, 3, 4, 8):
+            spans = [shard_rows(M, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == M
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(m0 % 128 == 0 or m0 == M for m0, _ in spans)
+    with pytest.raises(ValueError):
+        shard_rows(10, 2, 2)
+
+
+def _oracle_compute(seen):
+    from oracle import oracle
+
+    def compute(a, mat2, sa, sb, bias, sr, out_dtype, fast, *, profile, splitk, backend):
+        seen.append(splitk)
+        S, scheme = (1, "none") if splitk == 1 else splitk
+        name = str(out_dtype).replace("torch.", "")
+        bits = oracle.scaled_mm(a.view(torch.uint8).numpy(), mat2.t().contiguous().view(torch.uint8).numpy(),
+                                float(sa), float(sb), out=name, preset=profile.split("-")[0], fast=fast, S=S,
+                                scheme=scheme, threads=2)
+        it = {1: np.uint8, 2: np.int16, 4: np.int32}[bits.itemsize]
+        return torch.from_numpy(bits.view(it).copy()).view(out_dtype)
+    return compute
+
+
+def _worker(rank, world, port, M, N, K, profile, out_name, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from mmaemu_b200.sharding import sharded_scaled_mm
+    from oracle import oracle
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(3)
+        a = (torch.randn(M, K, generator=g) * 8).to(F8["e5m2"])
+        bt = (torch.randn(N, K, generator=g) * 8).to(F8["e4m3"])
+        od = getattr(torch, out_name)
+        seen = []
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            y = sharded_scaled_mm(a, bt.t(), torch.tensor(0.25), torch.tensor(3.0), out_dtype=od, use_fast_accum=True,
+                                  profile=profile, compute=_oracle_compute(seen))
+            from mmaemu_b200.splitk import resolve_splitk
+            d = resolve_splitk(M, N, K, a_dtype=a.dtype, b_dtype=bt.dtype, out_dtype=od, use_fast_accum=True,
+                               profile=profile)
+        want = oracle.scaled_mm(a.view(torch.uint8).numpy(), bt.view(torch.uint8).numpy(), 0.25, 3.0, out=out_name,
+                                fmt_a="e5m2", fmt_b="e4m3", preset=profile, fast=True, S=d.S, scheme=d.scheme)
+        it = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[y.element_size()]
+        got = y.contiguous().view(it).numpy().view(want.dtype)
+        ok = y.shape == (M, N) and np.array_equal(got, want) and seen == [1 if d.S == 1 else (d.S, d.scheme)]
+        q.put((rank, bool(ok), d.S))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def _oracle_compute_mixed(seen):
+    from oracle import oracle
+
+    def compute(a, mat2, sa, sb, bias, sr, out_dtype, fast, *, profile, splitk, backend):
+        seen.append(splitk)
+        S, scheme = (1, "none") if splitk == 1 else splitk
+        name = str(out_dtype).replace("torch.", "")
+        bits = oracle.scaled_mm(a.view(torch.uint8).numpy(), mat2.t().contiguous().view(torch.uint8).numpy(),
+                                float(sa), float(sb), out=name, fmt_a="e5m2", fmt_b="e4m3", preset=profile, fast=fast,
+                                S=S, scheme=scheme, threads=2)
+        it = {1: np.uint8, 2: np.int16, 4: np.int32}[bits.itemsize]
+        return torch.from_numpy(bits.view(it).copy()).view(out_dtype)
+    return compute
+
+
+_oracle_compute = _oracle_compute_mixed     # the workers use e5m2 x e4m3 operands
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("M,N,K,profile,out", [
+    (256, 64, 8192, "hopper", "float32"),        # equal slabs; the H100 table splits K for the full shape
+    (192, 64, 2048, "ada", "bfloat16"),          # ragged: rank 0 owns 128 rows, rank 1 owns 64; S = 3 by the table
+    (100, 192, 1024, "hopper", "float8_e5m2"),   # rank 1 owns nothing
+])
+def test_two_ranks_assemble_the_oracle_result(M, N, K, profile, out):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, M, N, K, profile, out, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    results = sorted(q.get(timeout=5) for _ in range(2))
+    assert [r[1] for r in results] == [True, True], results
