@@ -247,7 +247,8 @@ def run_ours(args) -> int:
         except Exception:  # noqa: BLE001
             pass
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        used = "fast" if kernel in ("auto", "fast") and args.fast_available else "integer"
+        auto = _lib.load().mmb200_kernel_for(a_dev.data_ptr(), K_, bt_dev.data_ptr(), K_, K_, NFMA, 1)
+        used = kernel if kernel != "auto" else ("fast" if auto == _lib.KERNEL_CODES["fast"] else "integer")
         clk_mhz = (clocks or {}).get("sm_mhz") or float(peaks.get("sm_max_mhz", 1965.0))
         issue_peak = 148 * 128 * clk_mhz * 1e6 / 1e12                 # T lane-instructions / s at the sampled SM clock
         per_gpu_macs = float(M_PER_GPU) * N_ * K_
@@ -302,9 +303,6 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    from mmaemu_b200 import _lib
-    L = _lib.load()
-    args.fast_available = False
     return run_ours(args)
 
 

@@ -101,6 +101,12 @@ int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void
                           int scheme, float scale_a, float scale_b, const float *scale_result /* host, nullable */,
                           int kernel, void *stream);
 
+/* Which kernel family a request with these operands and this plan runs on when `kernel` is MMB200_KERNEL_AUTO:
+ * MMB200_KERNEL_FAST or MMB200_KERNEL_INTEGER (the fast kernel needs 16-byte aligned operands, leading dimensions and K
+ * that are multiples of 16, and an unsplit plan). Pure host logic: no CUDA call, nothing is dereferenced. It has no
+ * counterpart in the reference, whose kernels each serve one format pair and one preset (mmaemu/backends/registry.py). */
+int mmb200_kernel_for(const void *A_dev, int64_t lda, const void *B_dev, int64_t ldb, int K, int nfma, int S);
+
 /* Number of kernel launches the library has issued in this process (all threads), for launch accounting. */
 int64_t mmb200_launch_count(void);
 

@@ -21,7 +21,8 @@ KERNEL_CODES = {"auto": 0, "integer": 1, "fast": 2}
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_ARCH, ERR_LAUNCH, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 
 EXPORTS = ("mmb200_abi_version", "mmb200_status_string", "mmb200_last_cuda_error", "mmb200_device_supported",
-           "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_launch_count")
+           "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_kernel_for",
+           "mmb200_launch_count")
 
 _lock = threading.Lock()
 _lib = None
@@ -68,6 +69,8 @@ def load():
         L.mmb200_scaled_mm_host.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, ci, ci, cf, cf,
                                             vp, ci, vp]
         L.mmb200_scaled_mm_host.restype = ci
+        L.mmb200_kernel_for.argtypes = [vp, i64, vp, i64, ci, ci, ci]
+        L.mmb200_kernel_for.restype = ci
         L.mmb200_launch_count.argtypes = []
         L.mmb200_launch_count.restype = i64
         got = L.mmb200_abi_version()

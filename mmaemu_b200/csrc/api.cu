@@ -181,6 +181,15 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
   return MMB200_OK;
 }
 
+int mmb200_kernel_for(const void* A, int64_t lda, const void* B, int64_t ldb, int K, int nfma, int S) {
+  mmb::Params p;
+  std::memset(&p, 0, sizeof(p));
+  p.A = static_cast<const uint8_t*>(A);
+  p.B = static_cast<const uint8_t*>(B);
+  p.lda = lda; p.ldb = ldb; p.K = K; p.S = S;
+  return mmb::fast_supports(p, nfma) ? MMB200_KERNEL_FAST : MMB200_KERNEL_INTEGER;
+}
+
 int64_t mmb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"
