@@ -161,7 +161,7 @@ def run_ours(args) -> int:
     sa_dev, sb_dev = sa.to(dev), sb.to(dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
-    kw = dict(out_dtype=torch.bfloat16, use_fast_accum=FAST, profile=PROFILE, backend=backend)
+    kw = dict(out_dtype=torch.bfloat16, use_fast_accum=FAST, profile=PROFILE, backend=backend, splitk=1)
 
     def step_resident():
         if world == 1:
@@ -204,8 +204,8 @@ def run_ours(args) -> int:
         oracle.build()
         y = step_resident()
         torch.cuda.synchronize(dev)
-        rows = torch.arange(0, M_PER_GPU, 331)[:12]
-        cols = torch.arange(0, N_, 97)[:40]
+        rows = torch.arange(0, M_PER_GPU, max(1, M_PER_GPU // 12 - 1))[:12]
+        cols = torch.arange(0, N_, max(1, N_ // 40 - 1))[:40]
         got = y[rows][:, cols].cpu().view(torch.int16).numpy().view(np.uint16)
         want = oracle.scaled_mm(a.view(torch.uint8).numpy()[rows.numpy()], bt.view(torch.uint8).numpy()[cols.numpy()],
                                 float(sa), float(sb), out="bfloat16", preset=NFMA, fast=FAST)
@@ -260,8 +260,9 @@ def run_ours(args) -> int:
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp32 round-toward-zero FMA + int32 (exact emulation of fp8 x fp8 blocks)"
             if used == "fast" else "int32", "data": "synthetic",
-            "config": {"workload": f"profile hopper, e4m3xe4m3, M={M_total} N={N_} K={K_} ({M_PER_GPU} rows per GPU), "
+            "config": {"workload": f"profile {PROFILE}, e4m3xe4m3, M={M_total} N={N_} K={K_} ({M_PER_GPU} rows per GPU), "
                                    f"bf16 out, split-K 1, use_fast_accum={FAST}, kernel {used}",
+                       "profile": PROFILE,
                        "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "multi_gpu": "row slabs + one NCCL all-gather per step" if world > 1 else "single GPU"},
             "roofline": {"bound": "alu-issue", "achieved": achieved_issue, "peak": issue_peak,
@@ -298,9 +299,20 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--kernel", choices=("auto", "integer", "fast"), default="auto")
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
+                    help="per-GPU problem size instead of the headline 4096 4096 4096 (profiling runs)")
+    ap.add_argument("--fast-accum", action="store_true", help="use_fast_accum=True instead of torch's default")
+    ap.add_argument("--profile", default=None, help="emulated platform profile (default hopper)")
     ap.add_argument("--skip-gate", action="store_true", help="skip the exactness gate before timing")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    global M_PER_GPU, N_, K_, FAST, PROFILE, NFMA
+    if args.shape:
+        M_PER_GPU, N_, K_ = args.shape
+    if args.fast_accum:
+        FAST = True
+    if args.profile:
+        PROFILE, NFMA = args.profile, (16 if args.profile.startswith("ada") else 32)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
