@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define MMB200_ABI_VERSION 1
+#define MMB200_ABI_VERSION 2
 
 /* status codes */
 #define MMB200_OK 0
@@ -100,6 +100,22 @@ int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void
                           void *D_host, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
                           int scheme, float scale_a, float scale_b, const float *scale_result /* host, nullable */,
                           int kernel, void *stream);
+
+/* Scratch memory. The fastest path decodes both operands once into device scratch memory (10 bytes per element of A,
+ * 8 per element of B, rounded up to 128 x 32 tiles) and streams the decoded tiles into shared memory with bulk
+ * asynchronous copies. mmb200_workspace_bytes gives the size for a shape; the *_ws entry points take the memory from
+ * the caller (128-byte aligned, at least that size, used only until the call's work on the stream has finished) and
+ * are otherwise identical to mmb200_scaled_mm / mmb200_accumulate. With workspace_dev == NULL, a workspace that is too
+ * small, or a request the fast kernels do not serve, they behave exactly like the entry points without workspace.
+ * The reference has no counterpart: its kernels decode inside the main loop (mmaemu/backends/cuda/csrc/h4.cu:190-211). */
+size_t mmb200_workspace_bytes(int M, int N, int K);
+int mmb200_scaled_mm_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
+                        void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
+                        int scheme, const float *scale_a_dev, const float *scale_b_dev, const float *scale_result_dev,
+                        int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
+int mmb200_accumulate_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
+                         float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                         int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
 
 /* Which kernel family a request with these operands and this plan runs on when `kernel` is MMB200_KERNEL_AUTO:
  * MMB200_KERNEL_FAST or MMB200_KERNEL_INTEGER (the fast kernel needs 16-byte aligned operands, leading dimensions and K

@@ -37,9 +37,11 @@ from .splitk import resolve_splitk
 
 __all__ = ["scaled_mm", "accumulate", "explain", "CallPlan", "BACKEND_NAMES"]
 
-BACKEND_NAMES = ("auto", "cuda", "cuda:b200", "cuda:b200-integer", "cuda:b200-fast")
+BACKEND_NAMES = ("auto", "cuda", "cuda:b200", "cuda:b200-integer", "cuda:b200-fast", "cuda:b200-direct")
+# kernel family behind each backend name; "direct" = automatic choice without scratch memory (operands are decoded
+# inside the main loop instead of once into a workspace)
 _KERNEL_OF = {"auto": "auto", "cuda": "auto", "cuda:b200": "auto", "cuda:b200-integer": "integer",
-              "cuda:b200-fast": "fast"}
+              "cuda:b200-fast": "fast", "cuda:b200-direct": "direct"}
 # dtypes torch 2.7.1 lets through its "is a float8 matrix" check before the zero-size early return
 _TORCH_FLOAT8 = {getattr(torch, n) for n in ("float8_e4m3fn", "float8_e5m2", "float8_e4m3fnuz", "float8_e5m2fnuz",
                                              "float8_e8m0fnu") if hasattr(torch, n)}
@@ -284,6 +286,22 @@ def _scalar_ptr(t: torch.Tensor, device) -> tuple:
     return t, t.data_ptr()
 
 
+def _workspace(L, kernel: str, a_ptr, lda, b_ptr, ldb, M, N, K, nfma, S, device):
+    """(keep-alive tensor or None, pointer or None, bytes) of the scratch memory for the staged fast kernel. The tensor
+    comes from torch's caching allocator, which hands it out again only to later work on the same stream."""
+    if kernel in ("integer", "direct") or os.environ.get("MMAEMU_B200_WORKSPACE", "1") == "0":
+        return None, None, 0
+    if L.mmb200_kernel_for(a_ptr, lda, b_ptr, ldb, K, nfma, S) != _lib.KERNEL_CODES["fast"]:
+        return None, None, 0
+    n = int(L.mmb200_workspace_bytes(M, N, K))
+    ws = torch.empty(n, dtype=torch.uint8, device=device)
+    return ws, ws.data_ptr(), n
+
+
+def _kernel_code(kernel: str) -> int:
+    return _lib.KERNEL_CODES["auto" if kernel == "direct" else kernel]
+
+
 def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -> torch.Tensor:
     dev = c.mat1.device
     a = c.mat1.detach()
@@ -296,12 +314,14 @@ def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -
     keep_r, pr = (None, None) if scale_result is None else _scalar_ptr(scale_result, dev)
     L = _lib.load()
     with torch.cuda.device(dev):
-        rc = L.mmb200_scaled_mm(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb, _lib.FMT_CODES[c.fb],
-                                y.data_ptr(), c.N, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K, c.preset.nfma,
-                                int(fast), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb, pr,
-                                _lib.KERNEL_CODES[c.kernel], _stream_ptr(dev))
-    _lib.check("mmb200_scaled_mm", rc)
-    del keep_a, keep_b, keep_r
+        ws, ws_ptr, ws_bytes = _workspace(L, c.kernel, a.data_ptr(), lda, bt.data_ptr(), ldb, c.M, c.N, c.K,
+                                          c.preset.nfma, c.decision.S, dev)
+        rc = L.mmb200_scaled_mm_ws(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb, _lib.FMT_CODES[c.fb],
+                                   y.data_ptr(), c.N, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K,
+                                   c.preset.nfma, int(fast), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb, pr,
+                                   _kernel_code(c.kernel), ws_ptr, ws_bytes, _stream_ptr(dev))
+    _lib.check("mmb200_scaled_mm_ws", rc)
+    del keep_a, keep_b, keep_r, ws
     return y
 
 
@@ -373,10 +393,13 @@ def accumulate(a, b, *, use_fast_accum, profile=None, splitk="auto", backend="au
     acc = torch.empty((M, N), dtype=torch.float32, device=dev)
     L = _lib.load()
     with torch.cuda.device(dev):
-        rc = L.mmb200_accumulate(au.data_ptr(), K, _lib.FMT_CODES[fa], bu.data_ptr(), K, _lib.FMT_CODES[fb],
-                                 acc.data_ptr(), N, M, N, K, preset.nfma, int(fast), decision.S,
-                                 _lib.SCHEME_CODES[scheme], _lib.KERNEL_CODES[kernel], _stream_ptr(dev))
-    _lib.check("mmb200_accumulate", rc)
+        ws, ws_ptr, ws_bytes = _workspace(L, kernel, au.data_ptr(), K, bu.data_ptr(), K, M, N, K, preset.nfma,
+                                          decision.S, dev)
+        rc = L.mmb200_accumulate_ws(au.data_ptr(), K, _lib.FMT_CODES[fa], bu.data_ptr(), K, _lib.FMT_CODES[fb],
+                                    acc.data_ptr(), N, M, N, K, preset.nfma, int(fast), decision.S,
+                                    _lib.SCHEME_CODES[scheme], _kernel_code(kernel), ws_ptr, ws_bytes, _stream_ptr(dev))
+    _lib.check("mmb200_accumulate_ws", rc)
+    del ws
     return acc
 
 

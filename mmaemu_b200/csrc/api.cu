@@ -29,7 +29,8 @@ int current_device_ok() {
 // Shared argument validation and dispatch of the three device-pointer entry points.
 int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D, int64_t ldd,
         int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme, const float* sa, const float* sb,
-        const float* sr, int epilogue, int patch, int kernel, void* stream) {
+        const float* sr, int epilogue, int patch, int kernel, void* stream, void* workspace = nullptr,
+        size_t workspace_bytes = 0) {
   if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
   if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
   if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
@@ -64,16 +65,22 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t err;
-  if (kernel == MMB200_KERNEL_FAST) {
-    if (!mmb::fast_supports(p, nfma)) return MMB200_ERR_UNSUPPORTED;
-    err = mmb::launch_fast(p, nfma, st);
-  } else if (kernel == MMB200_KERNEL_AUTO && mmb::fast_supports(p, nfma)) {
-    err = mmb::launch_fast(p, nfma, st);
+  int launches = 1;
+  const bool fast_ok = mmb::fast_supports(p, nfma);
+  if (kernel == MMB200_KERNEL_FAST && !fast_ok) return MMB200_ERR_UNSUPPORTED;
+  if (kernel != MMB200_KERNEL_INTEGER && fast_ok) {
+    const size_t need = mmb::staged_workspace_bytes(M, N, K);
+    if (workspace && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 127)) {
+      launches = 0;
+      err = mmb::launch_staged(p, nfma, workspace, workspace_bytes, st, &launches);
+    } else {
+      err = mmb::launch_fast(p, nfma, st);
+    }
   } else {
     err = mmb::launch_integer(p, nfma, st);
   }
   if (err != cudaSuccess) return cuda_fail(err);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  g_launches.fetch_add(launches, std::memory_order_relaxed);
   return MMB200_OK;
 }
 
@@ -131,6 +138,24 @@ int mmb200_scaled_mm(const void* A, int64_t lda, int fmt_a, const void* B, int64
   if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
   return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
              scale_result, 1, 1, kernel, stream);
+}
+
+size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K); }
+
+int mmb200_scaled_mm_ws(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
+                        int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                        const float* scale_a, const float* scale_b, const float* scale_result, int kernel,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
+  return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
+             scale_result, 1, 1, kernel, stream, workspace, workspace_bytes);
+}
+
+int mmb200_accumulate_ws(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, float* C,
+                         int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme, int kernel,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  return run(A, lda, fmt_a, B, ldb, fmt_b, C, ldc, MMB200_OUT_F32, M, N, K, nfma, fast, S, scheme, nullptr, nullptr,
+             nullptr, 0, 1, kernel, stream, workspace, workspace_bytes);
 }
 
 int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,

@@ -164,4 +164,8 @@ def test_launch_accounting():
     a, b, ta, tb = operands(16, 16, 64, seed=7)
     n0 = _lib.launch_count()
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
-    assert _lib.launch_count() == n0 + 1
+    assert _lib.launch_count() == n0 + 3              # two pre-decode kernels and the GEMM kernel (scratch memory path)
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1, backend="cuda:b200-direct")
+    assert _lib.launch_count() == n0 + 4              # one kernel that decodes in its main loop
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200")
+    assert _lib.launch_count() == n0 + 5              # split plans run on the integer kernel
