@@ -117,6 +117,19 @@ int mmb200_accumulate_ws(const void *A_dev, int64_t lda, int fmt_a, const void *
                          float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
                          int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* The scratch-memory path for callers that cannot allocate device memory and have none to lend: the scratch is a
+ * fixed array inside the library's device image, so the call performs no allocation of any kind. It serves what
+ * mmb200_scaled_mm_ws serves with its fast kernel (unsplit plan, K a multiple of 16, 16-byte aligned operands and
+ * leading dimensions; anything else returns MMB200_ERR_UNSUPPORTED) for shapes whose mmb200_workspace_bytes is at most
+ * MMB200_STATIC_SCRATCH_BYTES (larger ones return MMB200_ERR_TOO_LARGE). All calls on a device share the array: calls
+ * that overlap on the GPU race. The first call on a device looks up the array's address and should come before any
+ * stream capture. It has no counterpart in the reference, which allocates its outputs with torch. */
+#define MMB200_STATIC_SCRATCH_BYTES (64u << 20)
+int mmb200_scaled_mm_static(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
+                            void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast,
+                            const float *scale_a_dev, const float *scale_b_dev, const float *scale_result_dev,
+                            void *stream);
+
 /* Which kernel family a request with these operands and this plan runs on when `kernel` is MMB200_KERNEL_AUTO:
  * MMB200_KERNEL_FAST or MMB200_KERNEL_INTEGER (the fast kernel needs 16-byte aligned operands, leading dimensions and K
  * that are multiples of 16, and an unsplit plan). Pure host logic: no CUDA call, nothing is dereferenced. It has no

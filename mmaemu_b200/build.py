@@ -16,7 +16,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmmaemu_b200.so"
-SOURCES = ("api.cu", "kernel_integer.cu", "kernel_fast.cu")
+SOURCES = ("api.cu", "kernel_integer.cu", "kernel_fast.cu", "static_scratch.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--fmad=false", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 
