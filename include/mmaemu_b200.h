@@ -102,7 +102,7 @@ int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void
                           int kernel, void *stream);
 
 /* Scratch memory. The fastest path decodes both operands once into device scratch memory (10 bytes per element of A,
- * 8 per element of B, rounded up to 128 x 32 tiles) and streams the decoded tiles into shared memory with bulk
+ * 8.5 per element of B, rounded up to 128 x 32 tiles) and streams the decoded tiles into shared memory with bulk
  * asynchronous copies. mmb200_workspace_bytes gives the size for a shape; the *_ws entry points take the memory from
  * the caller (128-byte aligned, at least that size, used only until the call's work on the stream has finished) and
  * are otherwise identical to mmb200_scaled_mm / mmb200_accumulate. With workspace_dev == NULL, a workspace that is too

@@ -39,6 +39,7 @@ struct Params {
   int* ws_flag_b;
   int* status;
   int k_tiles;
+  int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
 };
 
 // ---------------------------------------------------------------------------------------------------------------

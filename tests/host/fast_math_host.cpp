@@ -72,3 +72,36 @@ extern "C" int fast_math_chains(const uint8_t* a, const uint8_t* b, int rows, in
   }
   return 0;
 }
+
+// Checks esum_from_power_sum for every block exponent E of E4M3 x E4M3 products and the extreme sums a tensor core
+// may return: the largest term alone, the exact sum of 32 largest terms with round-up slack, and random mixtures.
+// Returns the number of failures.
+extern "C" int fast_math_power_sum_check(void) {
+  int bad = 0;
+  uint32_t rng = 12345u;
+  for (int E = -12; E <= 16; ++E) {
+    const double top = std::ldexp(1.0, 6 * E);
+    const double cand[4] = {top, top * 32.0, top * 38.0, top * 63.9};
+    for (int c = 0; c < 4; ++c)
+      if (esum_from_power_sum((float)cand[c]) != (uint32_t)(E + 127) << 23) ++bad;
+    for (int trial = 0; trial < 200; ++trial) {
+      double s = top;
+      for (int k = 0; k < 31; ++k) {
+        rng = rng * 1664525u + 1013904223u;
+        const int e = E - (int)((rng >> 24) % 8);
+        if ((rng >> 8) & 1) s += std::ldexp(1.0, 6 * (e < -12 ? -12 : e));
+      }
+      if (esum_from_power_sum((float)s) != (uint32_t)(E + 127) << 23) ++bad;
+    }
+  }
+  if (esum_from_power_sum(0.0f) != 0u) ++bad;
+  // the power bytes of decode_bits: 127 + 6 ea for every nonzero E4M3 code, 0 for zero and NaN codes
+  for (uint32_t code = 0; code < 256; ++code) {
+    uint32_t ws, xb, tc, sg, cls, p64;
+    decode_bits<FMT_E4M3>(code * 0x01010101u, XBIAS_A, 0, 35, ws, xb, tc, sg, cls, &p64);
+    const uint32_t m = code & 0x7F, e = m >> 3;
+    const uint32_t want = (m == 0 || m == 0x7F) ? 0u : (uint32_t)(127 + 6 * ((e ? (int)e - 7 : -6)));
+    if (p64 != want * 0x01010101u) ++bad;
+  }
+  return bad;
+}

@@ -30,6 +30,7 @@ def lib():
     L = ctypes.CDLL(str(LIB))
     L.fast_math_chains.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_void_p]
     L.fast_math_chains.restype = ctypes.c_int
+    L.fast_math_power_sum_check.restype = ctypes.c_int
     return L
 
 
@@ -86,3 +87,9 @@ def test_nonfinite_codes_count_as_zero(lib):
                  for x, f in ((a, fa), (b, fb))]
         want = oracle.dot(clean[0].astype(np.uint8), clean[1].astype(np.uint8), None, fmt_a=fa, fmt_b=fb, preset=32)
         assert np.array_equal(chains(lib, a, b, fa, fb, 32), want)
+
+
+def test_tensor_core_exponent_pass_decode(lib):
+    """The exponent field read off a sum of powers 64^(ea + eb) is the block exponent for every sum a tensor core can
+    return, and the per-code powers are 2^(6 ea)."""
+    assert lib.fast_math_power_sum_check() == 0
