@@ -50,7 +50,9 @@ static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma
       uint32_t tt;
       float R = block_start<FA, FB>(acc, e2 << 7, tt);
       for (int c = 0; c < nfma; ++c) R = product(va[c], vb[c], R);
-      for (int g = 0; g < nfma / 4; ++g) R = fix_group(R, ta[g], sa[g], tb[g], sb[g], tt);
+      uint32_t n128 = 0;
+      for (int g = 0; g < nfma / 4; ++g) n128 = count_group(n128, ta[g], sa[g], tb[g], sb[g], tt);
+      R = apply_count(R, n128);
       acc = block_end(R);
       if (chain_len && (k0 + nfma) % chain_len == 0) { part = add_rn(part, chain_cut(acc)); acc = 0.0f; }
     }
