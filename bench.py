@@ -32,10 +32,10 @@ METRIC = "bit-exact emulated FP8 GEMM TFLOP/s (2MNK/t)"
 
 # Executed warp-instruction lanes per emulated multiply-accumulate of each kernel family, from the ncu captures
 # summarised under profiles/ (smsp__inst_executed.sum * 32 / (M*N*K) on the same workload).
-INST_PER_MAC = {"integer": None, "fast": 3.78, "staged": 3.57}
-# DRAM bytes per launch of the workload above from the same captures (dram__bytes_read.sum + dram__bytes_write.sum);
-# None until a capture exists.
-DRAM_TRAFFIC = {"integer": None, "fast": None, "staged": None}
+INST_PER_MAC = {"integer": None, "fast": 3.78, "staged": 2.86}
+# DRAM bytes per launch of the main kernel on the workload above, from a one-pass capture at full size
+# (dram__bytes_read.sum + dram__bytes_write.sum = 1,170,526,464 + 32,845,568); None where no capture exists.
+DRAM_TRAFFIC = {"integer": None, "fast": None, "staged": 1203372032}
 
 
 def make_operands(rank: int):
@@ -50,36 +50,79 @@ def make_operands(rank: int):
 
 
 class ClockSampler(threading.Thread):
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs: NVML every 5 ms when the
+    pynvml module is present, else one nvidia-smi query per 100 ms. Read-only; nothing on the GPU is changed."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
         super().__init__(daemon=True)
-        self.index, self.rows, self.stop_flag = index, [], threading.Event()
+        self.index, self.stop_flag = index, threading.Event()
+        self.sm, self.max_sm, self.power, self.seen = [], None, [], set()
 
-    def run(self):
+    def _nvml(self) -> bool:
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.index
+            if visible:
+                entry = visible.split(",")[self.index].strip()
+                if not entry.isdigit():
+                    return False
+                index = int(entry)
+            h = nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = int(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                    "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                    "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self.stop_flag.is_set():
+                self.sm.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                mask = int(reasons(h))
+                self.seen.update(n for n, b in bits.items() if mask & int(b))
+                try:
+                    self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                except Exception:  # noqa: BLE001
+                    pass
+                self.stop_flag.wait(0.005)
+            return True
+        except Exception:  # noqa: BLE001
+            return bool(self.sm)
+
+    def _smi(self):
         while not self.stop_flag.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                       "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-                self.rows.append([x.strip() for x in out.strip().split(",")])
+                r = [x.strip() for x in out.strip().split(",")]
+                if len(r) >= 7 and r[0].isdigit():
+                    self.sm.append(int(r[0]))
+                    self.max_sm = int(r[1]) if r[1].isdigit() else self.max_sm
+                    self.seen.update(n for i, n in enumerate(self.NAMES) if r[3 + i] == "Active")
             except Exception:  # noqa: BLE001
                 return
             self.stop_flag.wait(0.1)
 
+    def run(self):
+        if not self._nvml():
+            self._smi()
+
     def summary(self) -> dict:
         self.stop_flag.set()
         self.join(3)
-        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 7 and r[0].isdigit())
+        sm = sorted(self.sm)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in self.rows)]
-        mx = [int(r[1]) for r in self.rows if len(r) >= 7 and r[1].isdigit()]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"]}
+        out = {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.max_sm,
+               "reasons": [n for n in self.NAMES if n in self.seen], "samples": len(sm)}
+        if self.power:
+            out["power_w_median"] = sorted(self.power)[len(self.power) // 2]
+        return out
 
 
 def cpu_baseline(a_u8, bt_u8, sa: float, sb: float, seconds: float = 12.0) -> dict:

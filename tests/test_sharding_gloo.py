@@ -26,25 +26,10 @@ def test_shard_rows_cover_every_row_once():
         shard_rows(10, 2, 2)
 
 
-def _oracle_compute(seen):
-    from oracle import oracle
-
-    def compute(a, mat2, sa, sb, bias, sr, out_dtype, fast, *, profile, splitk, backend):
-        seen.append(splitk)
-        S, scheme = (1, "none") if splitk == 1 else splitk
-        name = str(out_dtype).replace("torch.", "")
-        bits = oracle.scaled_mm(a.view(torch.uint8).numpy(), mat2.t().contiguous().view(torch.uint8).numpy(),
-                                float(sa), float(sb), out=name, preset=profile.split("-")[0], fast=fast, S=S,
-                                scheme=scheme, threads=2)
-        it = {1: np.uint8, 2: np.int16, 4: np.int32}[bits.itemsize]
-        return torch.from_numpy(bits.view(it).copy()).view(out_dtype)
-    return compute
-
-
-def _worker(rank, world, port, M, N, K, profile, out_name, q):
+def _worker(rank, world, port, M, N, K, profile, out_name, local, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
-    from mmaemu_b200.sharding import sharded_scaled_mm
+    from mmaemu_b200.sharding import shard_rows, sharded_scaled_mm
     from oracle import oracle
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -55,8 +40,11 @@ def _worker(rank, world, port, M, N, K, profile, out_name, q):
         seen = []
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
-            y = sharded_scaled_mm(a, bt.t(), torch.tensor(0.25), torch.tensor(3.0), out_dtype=od, use_fast_accum=True,
-                                  profile=profile, compute=_oracle_compute(seen))
+            m0, m1 = shard_rows(M, world, rank)
+            extra = dict(input_is_local=True, full_rows=M) if local else {}      # only this rank's rows are passed
+            y = sharded_scaled_mm(a[m0:m1] if local else a, bt.t(), torch.tensor(0.25), torch.tensor(3.0),
+                                  out_dtype=od, use_fast_accum=True, profile=profile, compute=_oracle_compute(seen),
+                                  **extra)
             from mmaemu_b200.splitk import resolve_splitk
             d = resolve_splitk(M, N, K, a_dtype=a.dtype, b_dtype=bt.dtype, out_dtype=od, use_fast_accum=True,
                                profile=profile)
@@ -71,7 +59,7 @@ def _worker(rank, world, port, M, N, K, profile, out_name, q):
         dist.destroy_process_group()
 
 
-def _oracle_compute_mixed(seen):
+def _oracle_compute(seen):
     from oracle import oracle
 
     def compute(a, mat2, sa, sb, bias, sr, out_dtype, fast, *, profile, splitk, backend):
@@ -86,25 +74,24 @@ def _oracle_compute_mixed(seen):
     return compute
 
 
-_oracle_compute = _oracle_compute_mixed     # the workers use e5m2 x e4m3 operands
-
-
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("M,N,K,profile,out", [
-    (256, 64, 8192, "hopper", "float32"),        # equal slabs; the H100 table splits K for the full shape
-    (192, 64, 2048, "ada", "bfloat16"),          # ragged: rank 0 owns 128 rows, rank 1 owns 64; S = 3 by the table
-    (100, 192, 1024, "hopper", "float8_e5m2"),   # rank 1 owns nothing
+@pytest.mark.parametrize("M,N,K,profile,out,local", [
+    (256, 64, 8192, "hopper", "float32", False),        # equal slabs; the H100 table splits K for the full shape
+    (192, 64, 2048, "ada", "bfloat16", False),          # ragged: rank 0 owns 128 rows, rank 1 owns 64; S = 3 by the table
+    (100, 192, 1024, "hopper", "float8_e5m2", False),   # rank 1 owns nothing
+    (256, 64, 8192, "hopper", "bfloat16", True),        # every rank passes only its own slab (input_is_local)
+    (192, 64, 2048, "ada", "float32", True),
 ])
-def test_two_ranks_assemble_the_oracle_result(M, N, K, profile, out):
+def test_two_ranks_assemble_the_oracle_result(M, N, K, profile, out, local):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, M, N, K, profile, out, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, M, N, K, profile, out, local, q)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
