@@ -26,7 +26,9 @@ static float code_value(uint32_t code, int fmt) {      // value of a sanitised c
   return s ? -v : v;
 }
 
-template <int FA, int FB>
+// POW: the block exponent comes from a sum of products of powers, as the tensor-core exponent pass computes it
+// (E4M3 x E4M3 only; here the sum is taken in k order with round-to-nearest fp32 additions).
+template <int FA, int FB, bool POW = false>
 static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma, int chain_len, float* out) {
   using P = Pair<FA, FB>;
   const int Kp = (K + 31) / 32 * 32;
@@ -36,19 +38,32 @@ static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma
     float acc = 0.0f, part = 0.0f;
     for (int k0 = 0; k0 < Kp; k0 += nfma) {
       uint32_t ta[8], sa[8], tb[8], sb[8], xa[32], xbv[32];
-      float va[32], vb[32];
+      float va[32], vb[32], pwa[32], pwb[32];
       for (int g = 0; g < nfma / 4; ++g) {
-        uint32_t wa = 0, wb = 0, ws, xw, cls;
+        uint32_t wa = 0, wb = 0, ws, xw, cls, pw;
         for (int q = 0; q < 4; ++q) { wa |= (uint32_t)pa[k0 + 4 * g + q] << (8 * q); wb |= (uint32_t)pb[k0 + 4 * g + q] << (8 * q); }
-        decode_bits<FA>(wa, XBIAS_A, P::TADD_A, P::TZERO_A, ws, xw, ta[g], sa[g], cls);
-        for (int q = 0; q < 4; ++q) { xa[4 * g + q] = (xw >> (8 * q)) & 0xFF; va[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FA); }
-        decode_bits<FB>(wb, XBIAS_B, P::TADD_B, P::TZERO_B, ws, xw, tb[g], sb[g], cls);
-        for (int q = 0; q < 4; ++q) { xbv[4 * g + q] = (xw >> (8 * q)) & 0xFF; vb[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FB); }
+        decode_bits<FA>(wa, XBIAS_A, P::TADD_A, P::TZERO_A, ws, xw, ta[g], sa[g], cls, &pw, POW_BIAS_A);
+        for (int q = 0; q < 4; ++q) {
+          xa[4 * g + q] = (xw >> (8 * q)) & 0xFF; va[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FA);
+          pwa[4 * g + q] = u2f(((pw >> (8 * q)) & 0xFF) << 23);
+        }
+        decode_bits<FB>(wb, XBIAS_B, P::TADD_B, P::TZERO_B, ws, xw, tb[g], sb[g], cls, &pw, POW_BIAS_B);
+        for (int q = 0; q < 4; ++q) {
+          xbv[4 * g + q] = (xw >> (8 * q)) & 0xFF; vb[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FB);
+          pwb[4 * g + q] = u2f(((pw >> (8 * q)) & 0xFF) << 23);
+        }
       }
-      uint32_t e2 = 0;                                  // this output in the high half, a dummy neighbour in the low half
-      for (int c = 0; c < nfma; ++c) e2 = addmax16x2(xa[c] * 0x00010001u, (xbv[c] << 16) | 1u, e2);
       uint32_t tt;
-      float R = block_start<FA, FB>(acc, e2 << 7, tt);
+      float R;
+      if (POW) {
+        float S = 0.0f;
+        for (int c = 0; c < nfma; ++c) S = add_rn(S, pwa[c] * pwb[c]);
+        R = block_start_at<FA, FB>(acc, block_exponent_pow(acc, S), tt);
+      } else {
+        uint32_t e2 = 0;                                // this output in the high half, a dummy neighbour in the low half
+        for (int c = 0; c < nfma; ++c) e2 = addmax16x2(xa[c] * 0x00010001u, (xbv[c] << 16) | 1u, e2);
+        R = block_start<FA, FB>(acc, e2 << 7, tt);
+      }
       for (int c = 0; c < nfma; ++c) R = product(va[c], vb[c], R);
       uint32_t n128 = 0;
       for (int g = 0; g < nfma / 4; ++g) n128 = count_group(n128, ta[g], sa[g], tb[g], sb[g], tt);
@@ -65,6 +80,10 @@ static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma
 extern "C" int fast_math_chains(const uint8_t* a, const uint8_t* b, int rows, int K, int fa, int fb, int nfma,
                                 int chain_len, float* out) {
   if ((nfma != 16 && nfma != 32) || rows < 0 || K < 0 || (chain_len && chain_len % nfma)) return -1;
+  if (fa == 4 && fb == 4) {                            // format code 4: E4M3 with the power-sum exponent pass
+    chains<FMT_E4M3, FMT_E4M3, true>(a, b, rows, K, nfma, chain_len, out);
+    return 0;
+  }
   switch (fa * 2 + fb) {
     case 0: chains<FMT_E4M3, FMT_E4M3>(a, b, rows, K, nfma, chain_len, out); break;
     case 1: chains<FMT_E4M3, FMT_E5M2>(a, b, rows, K, nfma, chain_len, out); break;
@@ -75,35 +94,44 @@ extern "C" int fast_math_chains(const uint8_t* a, const uint8_t* b, int rows, in
   return 0;
 }
 
-// Checks esum_from_power_sum for every block exponent E of E4M3 x E4M3 products and the extreme sums a tensor core
-// may return: the largest term alone, the exact sum of 32 largest terms with round-up slack, and random mixtures.
-// Returns the number of failures.
+// Checks block_exponent_pow for every block exponent E of E4M3 x E4M3 products and the extreme sums a tensor core
+// may return: the largest term alone, sums of 32 largest terms with slack, and random mixtures; then the power bytes of
+// decode_bits. Returns the number of failures.
 extern "C" int fast_math_power_sum_check(void) {
   int bad = 0;
   uint32_t rng = 12345u;
   for (int E = -12; E <= 16; ++E) {
-    const double top = std::ldexp(1.0, 6 * E);
-    const double cand[4] = {top, top * 32.0, top * 38.0, top * 63.9};
-    for (int c = 0; c < 4; ++c)
-      if (esum_from_power_sum((float)cand[c]) != (uint32_t)(E + 127) << 23) ++bad;
+    const double top = std::ldexp(1.0, 8 * E - 7);
+    const double cand[5] = {top, top * 32.0, top * 38.0, top * 255.9, std::nextafter((float)(top * 256.0), 0.0f)};
+    const uint32_t want = (uint32_t)(E + 127) << 23;
+    for (int c = 0; c < 5; ++c)
+      if (block_exponent_pow(0.0f, (float)cand[c]) != want) ++bad;
     for (int trial = 0; trial < 200; ++trial) {
       double s = top;
       for (int k = 0; k < 31; ++k) {
         rng = rng * 1664525u + 1013904223u;
         const int e = E - (int)((rng >> 24) % 8);
-        if ((rng >> 8) & 1) s += std::ldexp(1.0, 6 * (e < -12 ? -12 : e));
+        if ((rng >> 8) & 1) s += std::ldexp(1.0, 8 * (e < -12 ? -12 : e) - 7);
       }
-      if (esum_from_power_sum((float)s) != (uint32_t)(E + 127) << 23) ++bad;
+      if (block_exponent_pow(0.0f, (float)s) != want) ++bad;
+      // an accumulator with a larger / smaller exponent than the products
+      if (block_exponent_pow(std::ldexp(-1.5f, E + 3), (float)s) != (uint32_t)(E + 3 + 127) << 23) ++bad;
+      if (block_exponent_pow(std::ldexp(1.99f, E - 1), (float)s) != want) ++bad;
+      if (block_exponent_pow(std::ldexp(-1.0f, E), (float)s) != want) ++bad;
     }
   }
-  if (esum_from_power_sum(0.0f) != 0u) ++bad;
-  // the power bytes of decode_bits: 127 + 6 ea for every nonzero E4M3 code, 0 for zero and NaN codes
+  if (block_exponent_pow(0.0f, 0.0f) != (112u << 23)) ++bad;                       // 2^-15: below every product
+  if (block_exponent_pow(std::ldexp(1.25f, -20), 0.0f) != (112u << 23)) ++bad;
+  if (block_exponent_pow(std::ldexp(-1.25f, -9), 0.0f) != (118u << 23)) ++bad;
   for (uint32_t code = 0; code < 256; ++code) {
-    uint32_t ws, xb, tc, sg, cls, p64;
-    decode_bits<FMT_E4M3>(code * 0x01010101u, XBIAS_A, 0, 35, ws, xb, tc, sg, cls, &p64);
     const uint32_t m = code & 0x7F, e = m >> 3;
-    const uint32_t want = (m == 0 || m == 0x7F) ? 0u : (uint32_t)(127 + 6 * ((e ? (int)e - 7 : -6)));
-    if (p64 != want * 0x01010101u) ++bad;
+    const int ea = e ? (int)e - 7 : -6;
+    for (int side = 0; side < 2; ++side) {
+      uint32_t ws, xb, tc, sg, cls, pw;
+      decode_bits<FMT_E4M3>(code * 0x01010101u, XBIAS_A, 0, 35, ws, xb, tc, sg, cls, &pw, side ? POW_BIAS_B : POW_BIAS_A);
+      const uint32_t want = (m == 0 || m == 0x7F) ? 0u : (uint32_t)(127 + 8 * ea - (side ? 0 : 7));
+      if (pw != want * 0x01010101u) ++bad;
+    }
   }
   return bad;
 }

@@ -17,7 +17,7 @@ from oracle import oracle
 HERE = Path(__file__).resolve().parent
 SRC = HERE / "host" / "fast_math_host.cpp"
 LIB = HERE / "host" / "_build" / "libfast_math_host.so"
-FMT = {"e4m3": 0, "e5m2": 1}
+FMT = {"e4m3": 0, "e5m2": 1, "e4m3-pow": 4}     # "e4m3-pow": block exponents from sums of powers (tensor-core pass)
 
 
 @pytest.fixture(scope="module")
@@ -55,6 +55,21 @@ def test_chains_equal_the_block_model(lib, cls, fmts, nfma):
         bad = np.nonzero(got != want)[0]
         assert bad.size == 0, f"{cls} K={K}: {bad.size} of {got.size} chains differ; row {bad[0]}: " \
                               f"{got[bad[0]]:#x} != {want[bad[0]]:#x}"
+
+
+@pytest.mark.parametrize("nfma", (16, 32))
+@pytest.mark.parametrize("cls", datagen.CLASSES)
+def test_power_sum_exponent_pass_equals_the_block_model(lib, cls, nfma):
+    rng = np.random.default_rng(len(cls) * 17 + nfma)
+    for K in (16, 48, 256, 1936, 8192):
+        a = datagen.codes(rng, 64, K, "e4m3", cls, 0)
+        b = datagen.codes(rng, 64, K, "e4m3", cls, 1)
+        want = oracle.dot(a, b, None, preset=nfma)
+        assert np.array_equal(chains(lib, a, b, "e4m3-pow", "e4m3-pow", nfma), want), (cls, K)
+        if K >= 256:
+            slow = np.array([oracle.accumulate(a[i:i + 1], b[i:i + 1], preset=nfma, fast=False)[0, 0] for i in range(8)])
+            got = chains(lib, a[:8], b[:8], "e4m3-pow", "e4m3-pow", nfma, chain_len=128)
+            assert np.array_equal(got, slow), (cls, K)
 
 
 def test_long_chains_with_growing_accumulators(lib):
