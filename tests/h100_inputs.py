@@ -127,3 +127,83 @@ def make_inputs(job: dict):
     a = make_codes(d["kind"], d["seed"], range(job["M"]), job["K"], job["fa"], 1, d.get("S"))
     b = make_codes(d["kind"], d["seed"], range(job["N"]), job["K"], job["fb"], 2, d.get("S"))
     return a, b
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The same generator on torch tensors (any device), for replaying the full recordings on a GPU: all values stay below
+# 2^63, so int64 arithmetic reproduces the uint64 arithmetic above. Checked against make_codes in
+# tests/test_oracle_golden.py.
+def _mix_t(x):
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & 0xFFFFFFFF
+    x = x ^ (x >> 15)
+    x = (x * 0x2C1B3C6D) & 0xFFFFFFFF
+    return x ^ (x >> 16)
+
+
+def _uniform32_t(seed, salt, stream, rows, cols):
+    r = _mix_t((rows ^ int(_key(seed, salt, stream))) & 0xFFFFFFFF)
+    return _mix_t((r[:, None] + cols[None, :] * 0x297A2D39 + stream * 0x632BE5AB) & 0xFFFFFFFF)
+
+
+def make_codes_torch(kind: str, seed: int, row0: int, row1: int, K: int, fmt: str, salt: int, S=None, device="cpu"):
+    """uint8 codes [row1 - row0, K] of rows row0..row1-1, as a torch tensor on `device`."""
+    import torch
+    rows = torch.arange(row0, row1, dtype=torch.int64, device=device)
+    cols = torch.arange(K, dtype=torch.int64, device=device)
+
+    def assemble(sgn, e, m):
+        if fmt == "e4m3":
+            return ((sgn << 7) | ((e + 7) << 3) | (m << 1)).to(torch.uint8)
+        return ((sgn << 7) | ((e + 15) << 2) | m).to(torch.uint8)
+    if kind == "randn40":
+        thr, codes = _normal_table(fmt)
+        thr_t = torch.from_numpy(thr.astype(np.int64)).to(device)
+        codes_t = torch.from_numpy(codes).to(device)
+        u = _uniform32_t(seed, salt, 0, rows, cols)
+        return codes_t[torch.searchsorted(thr_t, u, right=True)]
+    if kind == "adv":
+        T = -(-K // 64)
+        e = _uniform32_t(seed, salt, 1, rows, torch.arange(T, dtype=torch.int64, device=device)) % 12 - 6
+        e = e.repeat_interleave(64, dim=1)[:, :K]
+        u = _uniform32_t(seed, salt, 2, rows, cols)
+        return assemble((u >> 31) & 1, e, u & 3)
+    if kind == "adv_split":
+        if not S or S < 2:
+            raise ValueError("adv_split needs S >= 2")
+        T = -(-K // 64)
+        t, o = cols // 64, cols % 64
+        sp = t % S
+
+        def full(tt):
+            return (tt >= 0) & (tt < T) & ((tt + 1) * 64 <= K)
+        q = len(range(S - 1, T, S))
+        nm = max(1, q // 2)
+        j = t // S
+        mir = (sp == S - 1) & full(t) & full(t - (S - 1)) & (j < nm)
+        src = (sp == 0) & full(t) & full(t + (S - 1)) & (j < nm)
+        hc = torch.where(mir, (t - (S - 1)) * 64 + o, cols)
+        big = (mir | src)[None, :]
+        ue = _uniform32_t(seed, salt, 3, rows, hc)
+        u = _uniform32_t(seed, salt, 4, rows, hc)
+        e = torch.where(big, 2 + ue % 3, -6 + ue % 4)
+        sgn = (u >> 31) & 1
+        if salt == 1:
+            sgn = torch.where(mir[None, :], 1 - sgn, sgn)
+        return assemble(sgn, e, u & 3)
+    raise ValueError(kind)
+
+
+def make_inputs_torch(job: dict, device="cpu", chunk_elements: int = 1 << 24):
+    """(a [M, K], b [N, K]) uint8 code tensors of a recorded job on `device`, generated in row chunks."""
+    import torch
+    d = job["data"]
+    out = []
+    for n_rows, fmt, salt in ((job["M"], job["fa"], 1), (job["N"], job["fb"], 2)):
+        x = torch.empty((n_rows, job["K"]), dtype=torch.uint8, device=device)
+        step = max(1, chunk_elements // max(1, job["K"]))
+        for r0 in range(0, n_rows, step):
+            r1 = min(n_rows, r0 + step)
+            x[r0:r1] = make_codes_torch(d["kind"], d["seed"], r0, r1, job["K"], fmt, salt, d.get("S"), device)
+        out.append(x)
+    return out[0], out[1]
