@@ -17,8 +17,13 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmmaemu_b200.so"
 SOURCES = ("api.cu", "kernel_integer.cu", "kernel_fast.cu", "static_scratch.cu")
+# translation units: (source, extra defines). kernel_fast.cu is compiled once per FP8 format pair, in parallel.
+UNITS = (("api.cu", ()), ("kernel_integer.cu", ()), ("static_scratch.cu", ()),
+         ("kernel_fast.cu", ("-DMMB_PART=0",)), ("kernel_fast.cu", ("-DMMB_PART=1",)),
+         ("kernel_fast.cu", ("-DMMB_PART=2",)), ("kernel_fast.cu", ("-DMMB_PART=3",)))
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--fmad=false", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared"]
+              "-Xcompiler", "-fPIC"]
+OBJ = PKG / "csrc" / "_obj"
 
 
 def nvcc_path() -> str:
@@ -39,16 +44,31 @@ def stale() -> bool:
 def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not stale():
         return LIB
-    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIB),
-           *[str(CSRC / s) for s in SOURCES]]
     env = dict(os.environ)
     env.pop("CC", None)      # a CC without its support files in the environment must not leak into nvcc's host pass
     env.pop("CXX", None)
+    OBJ.mkdir(exist_ok=True)
+    nvcc = nvcc_path()
+    jobs = []
+    for i, (src, defines) in enumerate(UNITS):
+        obj = OBJ / f"{Path(src).stem}_{i}.o"
+        cmd = [nvcc, *NVCC_FLAGS, *defines, *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src), "-o", str(obj)]
+        jobs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)))
+    failed = None
+    for cmd, obj, proc in jobs:
+        out, _ = proc.communicate()
+        if verbose or proc.returncode:
+            sys.stderr.write(out)
+        if proc.returncode and failed is None:
+            failed = (proc.returncode, cmd)
+    if failed:
+        raise RuntimeError(f"nvcc failed ({failed[0]}): {' '.join(failed[1])}")
+    cmd = [nvcc, "-shared", "-o", str(LIB), *[str(obj) for _, obj, _ in jobs]]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env)
     if verbose or r.returncode:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode:
-        raise RuntimeError(f"nvcc failed ({r.returncode}): {' '.join(cmd)}")
+        raise RuntimeError(f"link failed ({r.returncode}): {' '.join(cmd)}")
     return LIB
 
 

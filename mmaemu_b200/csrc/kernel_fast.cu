@@ -685,14 +685,43 @@ cudaError_t launch_staged_fmt(const Params& p, cudaStream_t stream, int* launche
   return err;
 }
 
-template <int NFMA>
-cudaError_t dispatch_formats(const Params& p, cudaStream_t stream, bool staged, int* launches) {
-  constexpr int E4 = MMB200_FMT_E4M3, E5 = MMB200_FMT_E5M2;
+}  // namespace
+
+// One entry point per format pair, so that the pairs can be compiled as separate translation units (MMB_PART = the
+// pair's index fmt_a * 2 + fmt_b; undefined: everything in one unit). Part 0 also holds the functions below them.
+#define MMB_PAIR_FUNCTION(NAME, FA, FB)                                                                              \
+  cudaError_t NAME(const Params& p, int nfma, cudaStream_t stream, bool staged, int* launches) {                     \
+    if (nfma == 16) return staged ? launch_staged_fmt<16, FA, FB>(p, stream, launches) : launch_direct<16, FA, FB>(p, stream); \
+    return staged ? launch_staged_fmt<32, FA, FB>(p, stream, launches) : launch_direct<32, FA, FB>(p, stream);       \
+  }
+#if !defined(MMB_PART) || MMB_PART == 0
+MMB_PAIR_FUNCTION(launch_pair_e4m3_e4m3, MMB200_FMT_E4M3, MMB200_FMT_E4M3)
+#endif
+#if !defined(MMB_PART) || MMB_PART == 1
+MMB_PAIR_FUNCTION(launch_pair_e4m3_e5m2, MMB200_FMT_E4M3, MMB200_FMT_E5M2)
+#endif
+#if !defined(MMB_PART) || MMB_PART == 2
+MMB_PAIR_FUNCTION(launch_pair_e5m2_e4m3, MMB200_FMT_E5M2, MMB200_FMT_E4M3)
+#endif
+#if !defined(MMB_PART) || MMB_PART == 3
+MMB_PAIR_FUNCTION(launch_pair_e5m2_e5m2, MMB200_FMT_E5M2, MMB200_FMT_E5M2)
+#endif
+#undef MMB_PAIR_FUNCTION
+
+#if !defined(MMB_PART) || MMB_PART == 0
+cudaError_t launch_pair_e4m3_e4m3(const Params&, int, cudaStream_t, bool, int*);
+cudaError_t launch_pair_e4m3_e5m2(const Params&, int, cudaStream_t, bool, int*);
+cudaError_t launch_pair_e5m2_e4m3(const Params&, int, cudaStream_t, bool, int*);
+cudaError_t launch_pair_e5m2_e5m2(const Params&, int, cudaStream_t, bool, int*);
+
+namespace {
+
+cudaError_t dispatch_formats(const Params& p, int nfma, cudaStream_t stream, bool staged, int* launches) {
   switch (p.fmt_a * 2 + p.fmt_b) {
-    case 0: return staged ? launch_staged_fmt<NFMA, E4, E4>(p, stream, launches) : launch_direct<NFMA, E4, E4>(p, stream);
-    case 1: return staged ? launch_staged_fmt<NFMA, E4, E5>(p, stream, launches) : launch_direct<NFMA, E4, E5>(p, stream);
-    case 2: return staged ? launch_staged_fmt<NFMA, E5, E4>(p, stream, launches) : launch_direct<NFMA, E5, E4>(p, stream);
-    default: return staged ? launch_staged_fmt<NFMA, E5, E5>(p, stream, launches) : launch_direct<NFMA, E5, E5>(p, stream);
+    case 0: return launch_pair_e4m3_e4m3(p, nfma, stream, staged, launches);
+    case 1: return launch_pair_e4m3_e5m2(p, nfma, stream, staged, launches);
+    case 2: return launch_pair_e5m2_e4m3(p, nfma, stream, staged, launches);
+    default: return launch_pair_e5m2_e5m2(p, nfma, stream, staged, launches);
   }
 }
 
@@ -737,7 +766,7 @@ cudaError_t launch_fast(const Params& p_in, int nfma, cudaStream_t stream) {
   if (tiles <= 0) return cudaSuccess;
   if (tiles > 0x7FFFFFFFLL) return cudaErrorInvalidValue;
   int launches = 0;
-  return nfma == 16 ? dispatch_formats<16>(p, stream, false, &launches) : dispatch_formats<32>(p, stream, false, &launches);
+  return dispatch_formats(p, nfma, stream, false, &launches);
 }
 
 size_t staged_workspace_bytes(int M, int N, int K) {
@@ -760,7 +789,8 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
   p.status = reinterpret_cast<int*>(base + w.status);
   cudaError_t err = cudaMemsetAsync(base + w.flag_a, 0, w.total - w.flag_a, stream);   // row flags and status word
   if (err != cudaSuccess) return err;
-  return nfma == 16 ? dispatch_formats<16>(p, stream, true, launches) : dispatch_formats<32>(p, stream, true, launches);
+  return dispatch_formats(p, nfma, stream, true, launches);
 }
+#endif  // part 0
 
 }  // namespace mmb
