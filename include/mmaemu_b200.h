@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define MMB200_ABI_VERSION 2
+#define MMB200_ABI_VERSION 3
 
 /* status codes */
 #define MMB200_OK 0
@@ -109,6 +109,11 @@ int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void
  * small, or a request the fast kernels do not serve, they behave exactly like the entry points without workspace.
  * The reference has no counterpart: its kernels decode inside the main loop (mmaemu/backends/cuda/csrc/h4.cu:190-211). */
 size_t mmb200_workspace_bytes(int M, int N, int K);
+/* The same for a split-K plan with S splits (S = 1: as above). With that much scratch the staged fast kernels also walk
+ * split plans: they consume the k-tiles in the plan's order and keep the running total and the pair slot of the split
+ * reduction in the scratch memory (8 more bytes per output, rounded up to 128 x 128 tiles, plus the tile order). With
+ * less, split plans run on the integer kernel as they do without workspace. */
+size_t mmb200_workspace_bytes_split(int M, int N, int K, int S);
 int mmb200_scaled_mm_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
                         void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
                         int scheme, const float *scale_a_dev, const float *scale_b_dev, const float *scale_result_dev,
@@ -131,8 +136,9 @@ int mmb200_scaled_mm_static(const void *A_dev, int64_t lda, int fmt_a, const voi
                             void *stream);
 
 /* Which kernel family a request with these operands and this plan runs on when `kernel` is MMB200_KERNEL_AUTO:
- * MMB200_KERNEL_FAST or MMB200_KERNEL_INTEGER (the fast kernel needs 16-byte aligned operands, leading dimensions and K
- * that are multiples of 16, and an unsplit plan). Pure host logic: no CUDA call, nothing is dereferenced. It has no
+ * MMB200_KERNEL_FAST or MMB200_KERNEL_INTEGER (without scratch memory the fast kernel needs 16-byte aligned operands, leading
+ * dimensions and K that are multiples of 16, and an unsplit plan; with scratch memory of mmb200_workspace_bytes_split
+ * the *_ws entry points serve split plans on the fast kernels too). Pure host logic: no CUDA call, nothing is dereferenced. It has no
  * counterpart in the reference, whose kernels each serve one format pair and one preset (mmaemu/backends/registry.py). */
 int mmb200_kernel_for(const void *A_dev, int64_t lda, const void *B_dev, int64_t ldb, int K, int nfma, int S);
 

@@ -12,7 +12,7 @@ from pathlib import Path
 from .errors import BackendUnavailableError
 
 LIB_PATH = Path(__file__).resolve().parent / "libmmaemu_b200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 FMT_CODES = {"e4m3": 0, "e5m2": 1}
 OUT_CODES = {"float32": 0, "bfloat16": 1, "float16": 2, "float8_e4m3fn": 3, "float8_e5m2": 4}
@@ -22,7 +22,7 @@ OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_ARCH, ERR_LAUNCH, ERR_TOO_LARGE = 0, -1, -
 
 EXPORTS = ("mmb200_abi_version", "mmb200_status_string", "mmb200_last_cuda_error", "mmb200_device_supported",
            "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_kernel_for",
-           "mmb200_launch_count", "mmb200_workspace_bytes", "mmb200_scaled_mm_ws", "mmb200_accumulate_ws",
+           "mmb200_launch_count", "mmb200_workspace_bytes", "mmb200_workspace_bytes_split", "mmb200_scaled_mm_ws", "mmb200_accumulate_ws",
            "mmb200_scaled_mm_static")
 
 _lock = threading.Lock()
@@ -72,6 +72,8 @@ def load():
         L.mmb200_scaled_mm_host.restype = ci
         L.mmb200_workspace_bytes.argtypes = [ci, ci, ci]
         L.mmb200_workspace_bytes.restype = ctypes.c_size_t
+        L.mmb200_workspace_bytes_split.argtypes = [ci, ci, ci, ci]
+        L.mmb200_workspace_bytes_split.restype = ctypes.c_size_t
         L.mmb200_scaled_mm_ws.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp,
                                           ci, vp, ctypes.c_size_t, vp]
         L.mmb200_scaled_mm_ws.restype = ci

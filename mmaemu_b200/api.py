@@ -286,14 +286,19 @@ def _scalar_ptr(t: torch.Tensor, device) -> tuple:
     return t, t.data_ptr()
 
 
+SPLIT_WORKSPACE_LIMIT = 8 << 30
+
+
 def _workspace(L, kernel: str, a_ptr, lda, b_ptr, ldb, M, N, K, nfma, S, device):
     """(keep-alive tensor or None, pointer or None, bytes) of the scratch memory for the staged fast kernel. The tensor
     comes from torch's caching allocator, which hands it out again only to later work on the same stream."""
     if kernel in ("integer", "direct") or os.environ.get("MMAEMU_B200_WORKSPACE", "1") == "0":
         return None, None, 0
-    if L.mmb200_kernel_for(a_ptr, lda, b_ptr, ldb, K, nfma, S) != _lib.KERNEL_CODES["fast"]:
-        return None, None, 0
-    n = int(L.mmb200_workspace_bytes(M, N, K))
+    if L.mmb200_kernel_for(a_ptr, lda, b_ptr, ldb, K, nfma, 1) != _lib.KERNEL_CODES["fast"]:
+        return None, None, 0                 # operands the fast kernels cannot read: the integer kernel serves the call
+    n = int(L.mmb200_workspace_bytes_split(M, N, K, S))
+    if S > 1 and n > SPLIT_WORKSPACE_LIMIT:
+        return None, None, 0                 # split plans keep 8 bytes of scratch per output; very large ones run on the integer kernel
     ws = torch.empty(n, dtype=torch.uint8, device=device)
     return ws, ws.data_ptr(), n
 

@@ -66,16 +66,17 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t err;
   int launches = 1;
-  const bool fast_ok = mmb::fast_supports(p, nfma);
-  if (kernel == MMB200_KERNEL_FAST && !fast_ok) return MMB200_ERR_UNSUPPORTED;
-  if (kernel != MMB200_KERNEL_INTEGER && fast_ok) {
-    const size_t need = mmb::staged_workspace_bytes(M, N, K);
-    if (workspace && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 127)) {
-      launches = 0;
-      err = mmb::launch_staged(p, nfma, workspace, workspace_bytes, st, &launches);
-    } else {
-      err = mmb::launch_fast(p, nfma, st);
-    }
+  // fast kernels: every plan with enough scratch memory (staged), unsplit plans without; else the integer kernel
+  const bool direct_ok = mmb::fast_supports(p, nfma);
+  const bool staged_ok = mmb::staged_supports(p, nfma) && workspace &&
+                         workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S) &&
+                         !(reinterpret_cast<uintptr_t>(workspace) & 127);
+  if (kernel == MMB200_KERNEL_FAST && !direct_ok && !staged_ok) return MMB200_ERR_UNSUPPORTED;
+  if (kernel != MMB200_KERNEL_INTEGER && staged_ok) {
+    launches = 0;
+    err = mmb::launch_staged(p, nfma, workspace, workspace_bytes, st, &launches);
+  } else if (kernel != MMB200_KERNEL_INTEGER && direct_ok) {
+    err = mmb::launch_fast(p, nfma, st);
   } else {
     err = mmb::launch_integer(p, nfma, st);
   }
@@ -140,7 +141,8 @@ int mmb200_scaled_mm(const void* A, int64_t lda, int fmt_a, const void* B, int64
              scale_result, 1, 1, kernel, stream);
 }
 
-size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K); }
+size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K, 1); }
+size_t mmb200_workspace_bytes_split(int M, int N, int K, int S) { return mmb::staged_workspace_bytes(M, N, K, S); }
 
 int mmb200_scaled_mm_ws(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
                         int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,

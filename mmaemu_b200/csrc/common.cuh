@@ -40,6 +40,12 @@ struct Params {
   int* status;
   int k_tiles;
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
+  // split plans on the staged kernels: the order of the 32-element k-tiles (plan_sequence) and, per output tile, the
+  // running total and the pair slot of the split reduction (scratch memory)
+  const uint32_t* ws_seq;
+  int seq_len;
+  float* ws_tot;
+  float* ws_slot;
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -149,6 +155,43 @@ __host__ __device__ __forceinline__ void split_order(const Plan& p, int step, in
   }
 }
 
+// The plan as a flat sequence of 32-element k-tiles in the order they are consumed, for kernels that stream tiles:
+// entry = index of the k-tile (k / 32) | SEQ_CHAIN_END when a chain ends after it (slow accumulation: every `group` own
+// tiles of a split, and at the end of a split when tiles are pending) | SEQ_SPLIT_END + role (split_order) when the
+// split's partial is complete after it. A split without tiles gives one SEQ_EMPTY entry (its partial is +0). Returns
+// the number of entries; out == nullptr only counts.
+constexpr uint32_t SEQ_TILE_MASK = 0xFFFFFu, SEQ_CHAIN_END = 1u << 20, SEQ_SPLIT_END = 1u << 21, SEQ_EMPTY = 1u << 22;
+constexpr int SEQ_ROLE_SHIFT = 24, SEQ_KT = 32;
+__host__ __device__ inline int plan_sequence(const Plan& plan, int K, uint32_t* out) {
+  int n = 0;
+  for (int step = 0; step < plan.S; ++step) {
+    int s, role, first, end, tstep;
+    split_order(plan, step, s, role);
+    split_tiles(plan, s, first, end, tstep);
+    int cnt = 0, last = -1;
+    for (int t = first; t < end; t += tstep) {
+      const long long kbeg = (long long)t * plan.W;
+      const long long kend = kbeg + plan.W < (long long)K ? kbeg + plan.W : (long long)K;
+      for (long long k0 = kbeg; k0 < kend; k0 += SEQ_KT) {
+        if (out) out[n] = (uint32_t)(k0 / SEQ_KT);
+        last = n++;
+      }
+      if (plan.group && ++cnt == plan.group) {
+        if (out) out[last] |= SEQ_CHAIN_END;
+        cnt = 0;
+      }
+    }
+    if (last < 0) {
+      if (out) out[n] = SEQ_EMPTY;
+      last = n++;
+    } else if (plan.group && cnt) {
+      if (out) out[last] |= SEQ_CHAIN_END;
+    }
+    if (out) out[last] |= SEQ_SPLIT_END | ((uint32_t)role << SEQ_ROLE_SHIFT);
+  }
+  return n;
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // IEEE class of sum_k a[k] * b[k] over the original codes when it is not finite: NaN for any NaN operand, Inf * 0, or
 // +Inf and -Inf terms together, else +-Inf. Returns false when the sum is finite.
@@ -252,7 +295,8 @@ cudaError_t launch_fast(const Params& p, int nfma, cudaStream_t stream);
 bool fast_supports(const Params& p, int nfma);
 // Staged fast kernel: scratch bytes it needs for a shape, and the launch (pre-decode of both operands, then the GEMM).
 // `launches` is increased by the number of kernels launched.
-size_t staged_workspace_bytes(int M, int N, int K);
+bool staged_supports(const Params& p, int nfma);            // like fast_supports, any plan
+size_t staged_workspace_bytes(int M, int N, int K, int S = 1);
 cudaError_t launch_staged(const Params& p, int nfma, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                           int* launches);
 

@@ -26,11 +26,11 @@ def _dev(x):
     return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
 
 
-def _ws(L, M, N, K, kernel):
+def _ws(L, M, N, K, kernel, S=1):
     """Scratch memory for the staged kernel when `kernel` is 'staged' (a test-side name: automatic choice + workspace)."""
     if kernel != "staged":
         return None, None, 0, kernel
-    n = int(L.mmb200_workspace_bytes(M, N, K))
+    n = int(L.mmb200_workspace_bytes_split(M, N, K, S))
     ws = torch.empty(max(n, 1), dtype=torch.uint8, device=DEV)
     return ws, ws.data_ptr(), n, "auto"
 
@@ -47,7 +47,7 @@ def scaled_mm(a, b, scale_a, scale_b, *, out="bfloat16", fmt_a="e4m3", fmt_b="e4
     D = torch.full((M, max(N, 1)), -1 if OUT_TORCH[out] != torch.uint8 else 0xEE, dtype=OUT_TORCH[out], device=DEV)
     sc = torch.tensor([scale_a, scale_b, 1.0 if scale_result is None else scale_result], dtype=torch.float32,
                       device=DEV)
-    ws, ws_ptr, ws_bytes, kernel = _ws(L, M, N, K, kernel)
+    ws, ws_ptr, ws_bytes, kernel = _ws(L, M, N, K, kernel, S)
     rc = L.mmb200_scaled_mm_ws(A.data_ptr(), K + ld_pad, _lib.FMT_CODES[fmt_a], B.data_ptr(), K + ld_pad,
                                _lib.FMT_CODES[fmt_b], D.data_ptr(), max(N, 1), _lib.OUT_CODES[out], M, N, K, int(preset),
                                int(bool(fast)), int(S), _lib.SCHEME_CODES[scheme], sc.data_ptr(), sc.data_ptr() + 4,
@@ -64,7 +64,7 @@ def accumulate(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=True, S=1, s
     N = b.shape[0]
     A, B = _dev(a), _dev(b)
     C = torch.full((M, max(N, 1)), -1, dtype=torch.int32, device=DEV)
-    ws, ws_ptr, ws_bytes, kernel = _ws(L, M, N, K, kernel)
+    ws, ws_ptr, ws_bytes, kernel = _ws(L, M, N, K, kernel, S)
     rc = L.mmb200_accumulate_ws(A.data_ptr(), max(K, 1), _lib.FMT_CODES[fmt_a], B.data_ptr(), max(K, 1),
                                 _lib.FMT_CODES[fmt_b], C.data_ptr(), max(N, 1), M, N, K, int(preset), int(bool(fast)),
                                 int(S), _lib.SCHEME_CODES[scheme], _lib.KERNEL_CODES[kernel], ws_ptr, ws_bytes,

@@ -168,4 +168,6 @@ def test_launch_accounting():
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1, backend="cuda:b200-direct")
     assert _lib.launch_count() == n0 + 4              # one kernel that decodes in its main loop
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200")
-    assert _lib.launch_count() == n0 + 5              # split plans run on the integer kernel
+    assert _lib.launch_count() == n0 + 8              # split plan: pre-decode x 2, the tile order, the GEMM kernel
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200-direct")
+    assert _lib.launch_count() == n0 + 9              # without scratch memory split plans run on the integer kernel
