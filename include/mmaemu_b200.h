@@ -122,6 +122,25 @@ int mmb200_accumulate_ws(const void *A_dev, int64_t lda, int fmt_a, const void *
                          float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
                          int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* Quantise prologue fused into the staged path: the activations X [M, K] (MMB200_HP_F32 or MMB200_HP_BF16, row stride
+ * ldx elements, 16-byte aligned rows) are multiplied by *quant_scale_dev, clamped to +-448 and rounded to E4M3 (nearest
+ * even; for bf16 activations the scale and the product are first rounded to bf16, as torch's type promotion has it) -- bit for bit torch's
+ * (x * scale).clamp(-448, 448).to(torch.float8_e4m3fn) on a CUDA device (NaN gives 0x7F) -- inside the pass that
+ * decodes operand A, so the codes are never read back from memory before the GEMM. The codes are also written to
+ * A_codes_dev [M, K] (row stride lda, a multiple of 16; 16-byte aligned) for the caller to keep. Everything after that
+ * is mmb200_scaled_mm_ws with fmt_a = E4M3. Needs the scratch memory (mmb200_workspace_bytes_split) and K a positive
+ * multiple of 16: otherwise MMB200_ERR_UNSUPPORTED and nothing is written. With M or N zero nothing is written either.
+ * Replaces the separate quantisation pass of the reference's FP8 examples (examples/evo2_offload.py:124-129), which
+ * runs as torch operations before mmaemu.scaled_mm; the reference has no fused counterpart. */
+#define MMB200_HP_F32 1
+#define MMB200_HP_BF16 2
+int mmb200_quantize_scaled_mm_ws(const void *X_dev, int64_t ldx, int x_dtype, const float *quant_scale_dev,
+                                 void *A_codes_dev, int64_t lda, const void *B_dev, int64_t ldb, int fmt_b,
+                                 void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
+                                 int scheme, const float *scale_a_dev, const float *scale_b_dev,
+                                 const float *scale_result_dev, void *workspace_dev, size_t workspace_bytes,
+                                 void *stream);
+
 /* The scratch-memory path for callers that cannot allocate device memory and have none to lend: the scratch is a
  * fixed array inside the library's device image, so the call performs no allocation of any kind. It serves what
  * mmb200_scaled_mm_ws serves with its fast kernel (unsplit plan, K a multiple of 16, 16-byte aligned operands and

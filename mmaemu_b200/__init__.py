@@ -18,7 +18,7 @@ from .errors import (BackendFallbackWarning, BackendUnavailableError, Experiment
 __version__ = "0.1.0"
 
 _LAZY = {
-    "scaled_mm": ("mmaemu_b200.api", "scaled_mm"), "accumulate": ("mmaemu_b200.api", "accumulate"),
+    "scaled_mm": ("mmaemu_b200.api", "scaled_mm"), "quantized_scaled_mm": ("mmaemu_b200.api", "quantized_scaled_mm"), "accumulate": ("mmaemu_b200.api", "accumulate"),
     "explain": ("mmaemu_b200.api", "explain"), "CallPlan": ("mmaemu_b200.api", "CallPlan"),
     "resolve_splitk": ("mmaemu_b200.splitk", "resolve_splitk"), "SplitK": ("mmaemu_b200.splitk", "SplitK"),
     "SplitDecision": ("mmaemu_b200.splitk", "SplitDecision"),

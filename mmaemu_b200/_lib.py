@@ -23,7 +23,7 @@ OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_ARCH, ERR_LAUNCH, ERR_TOO_LARGE = 0, -1, -
 EXPORTS = ("mmb200_abi_version", "mmb200_status_string", "mmb200_last_cuda_error", "mmb200_device_supported",
            "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_kernel_for",
            "mmb200_launch_count", "mmb200_workspace_bytes", "mmb200_workspace_bytes_split", "mmb200_scaled_mm_ws", "mmb200_accumulate_ws",
-           "mmb200_scaled_mm_static")
+           "mmb200_scaled_mm_static", "mmb200_quantize_scaled_mm_ws")
 
 _lock = threading.Lock()
 _lib = None
@@ -77,6 +77,9 @@ def load():
         L.mmb200_scaled_mm_ws.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp,
                                           ci, vp, ctypes.c_size_t, vp]
         L.mmb200_scaled_mm_ws.restype = ci
+        L.mmb200_quantize_scaled_mm_ws.argtypes = [vp, i64, ci, vp, vp, i64, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci,
+                                                   ci, ci, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.mmb200_quantize_scaled_mm_ws.restype = ci
         L.mmb200_accumulate_ws.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, ci, ci, vp,
                                            ctypes.c_size_t, vp]
         L.mmb200_accumulate_ws.restype = ci

@@ -360,6 +360,65 @@ def scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_d
     return out
 
 
+def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=None, out_dtype=None,
+                        use_fast_accum=False, *, profile=None, splitk="auto", return_codes=False):
+    """scaled_mm on activations that are still in fp32 or bf16: the quantisation to E4M3,
+
+        xq = (x * quant_scale).clamp(-448, 448).to(torch.float8_e4m3fn)          # as torch computes it on a CUDA device
+        y  = scaled_mm(xq, mat2, scale_a, scale_b, ...)
+
+    runs inside the pass that decodes the first operand instead of as separate torch operations (the recipe of the
+    reference's FP8 examples, examples/evo2_offload.py:124-129 of astding/mmaemu: quant_scale = 448 / amax and
+    scale_a = 1 / quant_scale). x: [M, K] fp32 or bf16, unit stride along K; quant_scale: one-element fp32 tensor
+    (with bf16 activations torch's type promotion rounds it to bf16 before the multiplication, and so does this call).
+    Everything else, including every check and raise, is scaled_mm's, applied to the E4M3 tensor the call produces.
+    Returns y, or (y, xq) with return_codes=True. Activations whose rows are not 16-byte aligned are quantised by the
+    torch expression above and multiplied by a plain scaled_mm call."""
+    if not isinstance(x, torch.Tensor) or x.dtype not in (torch.float32, torch.bfloat16) or x.dim() != 2:
+        raise TypeError("quantized_scaled_mm(): x must be a 2-D fp32 or bf16 tensor")
+    if not isinstance(quant_scale, torch.Tensor) or quant_scale.numel() != 1 or quant_scale.dtype != torch.float32:
+        raise TypeError("quantized_scaled_mm(): quant_scale must be a one-element fp32 tensor")
+    if torch.is_grad_enabled() and x.requires_grad:
+        raise UnsupportedFeatureError("inference only: an input requires grad while grad mode is enabled")
+    M, K = x.shape
+    xq = torch.empty((M, K), dtype=torch.float8_e4m3fn, device=x.device)
+    c = _prepare(xq, mat2, scale_a, scale_b, None, scale_result, out_dtype, use_fast_accum, None, profile, splitk,
+                 "auto", dry=False)
+    xs = x.detach()
+    per16 = 4 if xs.dtype == torch.float32 else 8
+    fused = (not c.early and K % 16 == 0 and xs.stride(1) == 1 and xs.stride(0) % per16 == 0
+             and xs.data_ptr() % 16 == 0 and os.environ.get("MMAEMU_B200_WORKSPACE", "1") != "0")
+    L = _lib.load() if fused else None
+    if fused:
+        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+        dev = x.device
+        bt = mat2.detach().t()
+        ldb = bt.stride(0) if c.N > 1 else c.K
+        fused = bt.data_ptr() % 16 == 0 and ldb % 16 == 0
+    if not fused:
+        xq.copy_((xs * quant_scale.to(xs.device)).clamp(-448, 448).to(torch.float8_e4m3fn))
+        y = scaled_mm(xq, mat2, scale_a, scale_b, None, scale_result, out_dtype, use_fast_accum, profile=profile,
+                      splitk=splitk)
+        return (y, xq) if return_codes else y
+    y = torch.empty((c.M, c.N), dtype=c.od, device=dev)
+    keep_q, pq = _scalar_ptr(quant_scale, dev)
+    keep_a, pa = _scalar_ptr(scale_a, dev)
+    keep_b, pb = _scalar_ptr(scale_b, dev)
+    keep_r, pr = (None, None) if scale_result is None else _scalar_ptr(scale_result, dev)
+    with torch.cuda.device(dev):
+        n = int(L.mmb200_workspace_bytes_split(c.M, c.N, c.K, c.decision.S))
+        ws = torch.empty(n, dtype=torch.uint8, device=dev)
+        rc = L.mmb200_quantize_scaled_mm_ws(xs.data_ptr(), xs.stride(0) if c.M > 1 else c.K,
+                                            1 if xs.dtype == torch.float32 else 2, pq, xq.data_ptr(), c.K, bt.data_ptr(),
+                                            ldb, _lib.FMT_CODES[c.fb], y.data_ptr(), c.N,
+                                            _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K, c.preset.nfma,
+                                            int(bool(use_fast_accum)), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb,
+                                            pr, ws.data_ptr(), n, _stream_ptr(dev))
+    _lib.check("mmb200_quantize_scaled_mm_ws", rc)
+    del keep_q, keep_a, keep_b, keep_r, ws
+    return (y, xq) if return_codes else y
+
+
 def accumulate(a, b, *, use_fast_accum, profile=None, splitk="auto", backend="auto",
                out_dtype_for_split=torch.float32):
     """fp32 [M, N] accumulator of a [M, K] x b [N, K]^T before alpha, as the profile's cuBLAS computes it (the

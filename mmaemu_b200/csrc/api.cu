@@ -30,7 +30,8 @@ int current_device_ok() {
 int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D, int64_t ldd,
         int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme, const float* sa, const float* sb,
         const float* sr, int epilogue, int patch, int kernel, void* stream, void* workspace = nullptr,
-        size_t workspace_bytes = 0) {
+        size_t workspace_bytes = 0, const void* a_hp = nullptr, int64_t ld_hp = 0, int hp_dtype = 0,
+        const float* quant_scale = nullptr) {
   if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
   if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
   if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
@@ -39,6 +40,10 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   if (S > 1 && scheme == MMB200_SCHEME_NONE) return MMB200_ERR_BAD_ARG;
   if (S > MMB200_MAX_SPLITS) return MMB200_ERR_TOO_LARGE;
   if (kernel < MMB200_KERNEL_AUTO || kernel > MMB200_KERNEL_FAST) return MMB200_ERR_BAD_ARG;
+  if (a_hp) {                                   // quantise prologue: E4M3 codes of A are produced by the call
+    if (hp_dtype != MMB200_HP_F32 && hp_dtype != MMB200_HP_BF16) return MMB200_ERR_BAD_ARG;
+    if (fmt_a != MMB200_FMT_E4M3 || !quant_scale || ld_hp < K) return MMB200_ERR_BAD_ARG;
+  }
   if (M == 0 || N == 0) return MMB200_OK;
   if (!D || ldd < N) return MMB200_ERR_BAD_ARG;
   if (K > 0 && (!A || !B || lda < K || ldb < K)) return MMB200_ERR_BAD_ARG;
@@ -66,12 +71,22 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t err;
   int launches = 1;
+  if (a_hp) {
+    p.a_hp = a_hp;
+    p.ld_hp = ld_hp;
+    p.a_hp_dtype = hp_dtype;
+    p.a_quant_scale = quant_scale;
+    p.a_codes = static_cast<uint8_t*>(const_cast<void*>(A));
+    const int per16 = hp_dtype == MMB200_HP_F32 ? 4 : 8;      // elements per 16 bytes
+    if ((reinterpret_cast<uintptr_t>(a_hp) & 15) || (ld_hp % per16) != 0) return MMB200_ERR_UNSUPPORTED;
+  }
   // fast kernels: every plan with enough scratch memory (staged), unsplit plans without; else the integer kernel
   const bool direct_ok = mmb::fast_supports(p, nfma);
   const bool staged_ok = mmb::staged_supports(p, nfma) && workspace &&
                          workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S) &&
                          !(reinterpret_cast<uintptr_t>(workspace) & 127);
   if (kernel == MMB200_KERNEL_FAST && !direct_ok && !staged_ok) return MMB200_ERR_UNSUPPORTED;
+  if (a_hp && (!staged_ok || kernel == MMB200_KERNEL_INTEGER)) return MMB200_ERR_UNSUPPORTED;   // only the pre-decode pass quantises
   if (kernel != MMB200_KERNEL_INTEGER && staged_ok) {
     launches = 0;
     err = mmb::launch_staged(p, nfma, workspace, workspace_bytes, st, &launches);
@@ -151,6 +166,17 @@ int mmb200_scaled_mm_ws(const void* A, int64_t lda, int fmt_a, const void* B, in
   if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
   return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
              scale_result, 1, 1, kernel, stream, workspace, workspace_bytes);
+}
+
+int mmb200_quantize_scaled_mm_ws(const void* X, int64_t ldx, int x_dtype, const float* quant_scale, void* A_codes,
+                                 int64_t lda, const void* B, int64_t ldb, int fmt_b, void* D, int64_t ldd, int out_dtype,
+                                 int M, int N, int K, int nfma, int fast, int S, int scheme, const float* scale_a,
+                                 const float* scale_b, const float* scale_result, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  if (!scale_a || !scale_b || !X || !A_codes) return MMB200_ERR_BAD_ARG;
+  return run(A_codes, lda, MMB200_FMT_E4M3, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a,
+             scale_b, scale_result, 1, 1, MMB200_KERNEL_AUTO, stream, workspace, workspace_bytes, X, ldx, x_dtype,
+             quant_scale);
 }
 
 int mmb200_accumulate_ws(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, float* C,

@@ -324,6 +324,51 @@ __global__ void __launch_bounds__(THREADS, 1) fast_kernel(const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Quantise prologue (the scalar conversion is fm::quantise_e4m3 in fast_math.cuh).
+// The 16 codes of row `row` starting at element k of one operand: the caller's FP8 codes, or -- operand A with the
+// quantise prologue -- the codes of 16 activations, which are also written to the codes array.
+template <bool IS_A>
+__device__ __forceinline__ uint4 load_codes16(const Params& p, int row, int rows, int k) {
+  if (row >= rows || k >= p.K) return make_uint4(0, 0, 0, 0);
+  if (!IS_A || !p.a_hp)
+    return __ldg(reinterpret_cast<const uint4*>((IS_A ? p.A : p.B) + (long long)row * (IS_A ? p.lda : p.ldb) + k));
+  const float scale = __ldg(p.a_quant_scale);
+  float x[16];
+  if (p.a_hp_dtype == MMB200_HP_F32) {
+    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.a_hp) + (long long)row * p.ld_hp + k);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 f = __ldg(src + q);
+      x[4 * q] = __fmul_rn(f.x, scale); x[4 * q + 1] = __fmul_rn(f.y, scale);
+      x[4 * q + 2] = __fmul_rn(f.z, scale); x[4 * q + 3] = __fmul_rn(f.w, scale);
+    }
+  } else {                        // bf16: torch multiplies in bf16 -- the scale and the product are rounded to bf16
+    const float scale_b = __uint_as_float((uint32_t)f32_to_bf16_bits(scale) << 16);
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.a_hp) + (long long)row * p.ld_hp + k);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 w = __ldg(src + q);
+      const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float lo = __fmul_rn(__uint_as_float(ws[h] << 16), scale_b);
+        const float hi = __fmul_rn(__uint_as_float(ws[h] & 0xFFFF0000u), scale_b);
+        x[8 * q + 2 * h] = __uint_as_float((uint32_t)f32_to_bf16_bits(lo) << 16);
+        x[8 * q + 2 * h + 1] = __uint_as_float((uint32_t)f32_to_bf16_bits(hi) << 16);
+      }
+    }
+  }
+  uint32_t w4[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    w4[q] = fm::quantise_e4m3(x[4 * q]) | (fm::quantise_e4m3(x[4 * q + 1]) << 8) | (fm::quantise_e4m3(x[4 * q + 2]) << 16) |
+            (fm::quantise_e4m3(x[4 * q + 3]) << 24);
+  const uint4 codes = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  *reinterpret_cast<uint4*>(p.a_codes + (long long)row * p.lda + k) = codes;
+  return codes;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // predecode_kernel: one CTA per (128-row block, k-tile) of one operand; writes the decoded tile to scratch memory and
 // ORs the non-finite classes of every row into the row-flag array (zeroed by the host before the launch).
 template <int FA, int FB, bool IS_A>
@@ -331,13 +376,10 @@ __global__ void __launch_bounds__(THREADS) predecode_kernel(const __grid_constan
   using Tile = typename std::conditional<IS_A, TileA, TileB>::type;
   const int tid = threadIdx.x, kt = blockIdx.x, rb = blockIdx.y;
   const int rows = IS_A ? p.M : p.N;
-  const uint8_t* src = IS_A ? p.A : p.B;
-  const long long ld = IS_A ? p.lda : p.ldb;
   Tile& tile = reinterpret_cast<Tile*>(IS_A ? p.ws_a : p.ws_b)[(long long)rb * p.k_tiles + kt];
   int* flags = IS_A ? p.ws_flag_a : p.ws_flag_b;
   const int lrow = tid % 128, lhalf = tid / 128, row = rb * 128 + lrow, k = kt * KT + 16 * lhalf;
-  const uint4 raw = (row < rows && k < p.K) ? __ldg(reinterpret_cast<const uint4*>(src + (long long)row * ld + k))
-                                            : make_uint4(0, 0, 0, 0);
+  const uint4 raw = load_codes16<IS_A>(p, row, rows, k);
   const uint32_t cls = decode16<FA, FB, IS_A>(raw, tile, lrow, 16 * lhalf);
   if (cls) atomicOr(&flags[row], (int)cls);
 }
@@ -483,13 +525,10 @@ __global__ void __launch_bounds__(THREADS) predecode_tc_kernel(const __grid_cons
   using P = fm::Pair<E4, E4>;
   const int tid = threadIdx.x, kt = blockIdx.x, rb = blockIdx.y;
   const int rows = IS_A ? p.M : p.N;
-  const uint8_t* src = IS_A ? p.A : p.B;
-  const long long ld = IS_A ? p.lda : p.ldb;
   TileTC& tile = reinterpret_cast<TileTC*>(IS_A ? p.ws_a : p.ws_b)[(long long)rb * p.k_tiles + kt];
   int* flags = IS_A ? p.ws_flag_a : p.ws_flag_b;
   const int lrow = tid % 128, lhalf = tid / 128, row = rb * 128 + lrow, k0 = kt * KT + 16 * lhalf;
-  const uint4 raw = (row < rows && k0 < p.K) ? __ldg(reinterpret_cast<const uint4*>(src + (long long)row * ld + k0))
-                                             : make_uint4(0, 0, 0, 0);
+  const uint4 raw = load_codes16<IS_A>(p, row, rows, k0);
   const int pos = IS_A ? pos_a(lrow) : pos_b(lrow);
   const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t seen = 0;

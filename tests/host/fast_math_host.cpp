@@ -135,3 +135,8 @@ extern "C" int fast_math_power_sum_check(void) {
   }
   return bad;
 }
+
+// E4M3 codes of n already scaled values (the quantise prologue's scalar step).
+extern "C" void fast_math_quantise_e4m3(const float* v, int n, uint8_t* out) {
+  for (int i = 0; i < n; ++i) out[i] = (uint8_t)quantise_e4m3(v[i]);
+}

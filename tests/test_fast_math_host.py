@@ -108,3 +108,23 @@ def test_tensor_core_exponent_pass_decode(lib):
     """The exponent field read off a sum of powers 64^(ea + eb) is the block exponent for every sum a tensor core can
     return, and the per-code powers are 2^(6 ea)."""
     assert lib.fast_math_power_sum_check() == 0
+
+
+def test_quantise_prologue_equals_torch(lib):
+    """quantise_e4m3 against torch's clamp + conversion on the CPU: every fp32 value with a 12-bit mantissa prefix across
+    the whole exponent range (all rounding ties of the E4M3 grid among them), random values, zeros, infinities, NaN."""
+    import torch
+    rng = np.random.default_rng(3)
+    hi = (np.arange(1 << 21, dtype=np.uint32) << 11)                     # sign, exponent, 12 mantissa bits
+    spots = np.array([0x00000000, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00000, 0x43E00000, 0x43E80000,
+                      0x43F00000, 0x3A800000, 0x3A000000, 0x39800000, 0x3A400000, 0x3AC00000], dtype=np.uint32)
+    rnd = rng.integers(0, 1 << 32, 1 << 20, dtype=np.uint64).astype(np.uint32)
+    near = (rng.standard_normal(1 << 20) * 64).astype(np.float32).view(np.uint32)
+    bits = np.concatenate([hi, spots, rnd, near])
+    v = bits.view(np.float32)
+    out = np.zeros(v.size, np.uint8)
+    lib.fast_math_quantise_e4m3.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    lib.fast_math_quantise_e4m3(v.ctypes.data, v.size, out.ctypes.data)
+    want = torch.from_numpy(v.copy()).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    bad = np.nonzero(out != want)[0]
+    assert bad.size == 0, f"{bad.size} differ; first {bits[bad[0]]:#010x}: {out[bad[0]]:#x} != {want[bad[0]]:#x}"

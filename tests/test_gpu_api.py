@@ -171,3 +171,81 @@ def test_launch_accounting():
     assert _lib.launch_count() == n0 + 8              # split plan: pre-decode x 2, the tile order, the GEMM kernel
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200-direct")
     assert _lib.launch_count() == n0 + 9              # without scratch memory split plans run on the integer kernel
+
+
+def test_call_is_capturable_in_a_cuda_graph():
+    """No host synchronisation anywhere in the call (scales and non-finite flags stay on the device), so a scaled_mm
+    call can be captured once and replayed on new operand values -- the gap the reference documents for its CUDA path
+    (docs/backends.md:116-117 of astding/mmaemu). The replay must equal eager calls bit for bit, also when the new
+    operands hold NaN codes and when the plan is split."""
+    M, N, K = 192, 256, 2048
+    rng = np.random.default_rng(21)
+    a0 = datagen._round_to(rng.standard_normal((M, K)) * 4, "e4m3")
+    b0 = datagen._round_to(rng.standard_normal((N, K)) * 4, "e4m3")
+    ta = torch.from_numpy(a0).to(DEV).view(F8["e4m3"])
+    tb = torch.from_numpy(b0).to(DEV).view(F8["e4m3"])
+    sa, sb = torch.tensor(0.5, device=DEV), torch.tensor(2.0, device=DEV)
+    for profile, split in (("hopper", 1), ("ada", (3, "pairwise"))):
+        kw = dict(out_dtype=torch.bfloat16, profile=profile, splitk=split)
+        mm.scaled_mm(ta, tb.t(), sa, sb, **kw)                     # warm-up outside the capture
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = mm.scaled_mm(ta, tb.t(), sa, sb, **kw)
+        for trial in range(3):
+            a1 = datagen._round_to(rng.standard_normal((M, K)) * 4, "e4m3")
+            b1 = datagen._round_to(rng.standard_normal((N, K)) * 4, "e4m3")
+            if trial == 2:
+                a1[5, 77] = 0x7F                                    # a NaN row
+                b1[9, 3] = 0xFF                                     # and a NaN column
+            ta.view(torch.uint8).copy_(torch.from_numpy(a1))
+            tb.view(torch.uint8).copy_(torch.from_numpy(b1))
+            sa.fill_(0.25 * (trial + 1))
+            g.replay()
+            torch.cuda.synchronize()
+            want = oracle.scaled_mm(a1, b1, 0.25 * (trial + 1), 2.0, out="bfloat16", preset=profile, fast=False,
+                                    S=1 if split == 1 else split[0], scheme="none" if split == 1 else split[1])
+            assert np.array_equal(bits(y), want), (profile, trial)
+
+
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16), ids=("fp32", "bf16"))
+def test_quantised_activations(dtype):
+    """quantized_scaled_mm: the E4M3 codes equal torch's (x * s).clamp(-448, 448).to(float8_e4m3fn) on the device, and
+    the product equals scaled_mm on those codes (checked against the oracle), for contiguous and padded activations,
+    an unsplit and a split plan, and the unfused fallback (rows that are not 16-byte aligned)."""
+    rng = np.random.default_rng(31)
+    for (M, N, K, pad, profile, split) in ((200, 192, 1024, 0, "hopper-te", 1), (64, 128, 2048, 24, "ada", (4, "serial")),
+                                           (33, 48, 1008, 3, "hopper", 1)):
+        x = rng.standard_normal((M, K + pad)).astype(np.float32)
+        x[3, 5], x[7, 9], x[11, 2], x[13, 1] = 1e9, -np.inf, np.nan, 1e-12       # clamp, -inf, NaN, underflow
+        x[1, :8] = [0.0, -0.0, 2.0 ** -20, -2.0 ** -19, 3.0, -3.0, 0.05, 100.0]
+        xt = torch.from_numpy(x).to(DEV).to(dtype)[:, :K]
+        finite = torch.where(torch.isfinite(xt) & (xt.abs() < 1e6), xt.abs().float(), torch.zeros((), device=DEV))
+        qs = (448.0 / finite.max()).to(torch.float32)
+        w = datagen._round_to(rng.standard_normal((N, K)) * 0.02 * 448 / 0.08, "e4m3")
+        tw = torch.from_numpy(w).to(DEV).view(F8["e4m3"])
+        sa, sb = (1.0 / qs).to(torch.float32), torch.tensor(0.08 / 448, device=DEV)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            y, xq = mm.quantized_scaled_mm(xt, qs, tw.t(), sa, sb, out_dtype=torch.bfloat16, profile=profile,
+                                           splitk=split, return_codes=True)
+        want_q = (xt * qs).clamp(-448, 448).to(torch.float8_e4m3fn)
+        assert torch.equal(xq.view(torch.uint8), want_q.view(torch.uint8)), (M, N, K, dtype)
+        codes = xq.view(torch.uint8).cpu().numpy()
+        assert codes[11, 2] == 0x7F and codes[3, 5] == 0x7E and codes[7, 9] == 0xFE and codes[13, 1] == 0x00
+        S, scheme = (1, "none") if split == 1 else split
+        want = oracle.scaled_mm(codes, w, float(sa), float(sb), out="bfloat16", preset=profile.split("-")[0], fast=False,
+                                S=S, scheme=scheme)
+        assert np.array_equal(bits(y), want), (M, N, K, dtype)
+
+
+def test_quantised_activations_argument_checks():
+    x = torch.zeros(16, 32, device=DEV)
+    w = torch.zeros(16, 32, device=DEV).to(torch.float8_e4m3fn)
+    one = torch.ones((), device=DEV)
+    with pytest.raises(TypeError):
+        mm.quantized_scaled_mm(x.half(), one, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1)
+    with pytest.raises(TypeError):
+        mm.quantized_scaled_mm(x, 2.0, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1)
+    with pytest.raises(mm.SplitKUnknownError):                      # scaled_mm's own checks apply to the produced tensor
+        mm.quantized_scaled_mm(x, one, w.t(), one, one, out_dtype=torch.bfloat16, profile="hopper")
