@@ -112,7 +112,10 @@ size_t mmb200_workspace_bytes(int M, int N, int K);
 /* The same for a split-K plan with S splits (S = 1: as above). With that much scratch the staged fast kernels also walk
  * split plans: they consume the k-tiles in the plan's order and keep the running total and the pair slot of the split
  * reduction in the scratch memory (8 more bytes per output, rounded up to 128 x 128 tiles, plus the tile order). With
- * less, split plans run on the integer kernel as they do without workspace. */
+ * less, split plans run on the integer kernel as they do without workspace. For shapes with few 128 x 128 output tiles the
+ * size also covers the chain results of K-sliced execution (plans with several chains are spread over the SMs along K and
+ * summed in the plan's order by a second kernel; up to 4 GiB, not used when the workspace is smaller or when
+ * $MMAEMU_B200_SLICES is 0). */
 size_t mmb200_workspace_bytes_split(int M, int N, int K, int S);
 int mmb200_scaled_mm_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
                         void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,

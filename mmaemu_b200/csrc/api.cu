@@ -83,7 +83,7 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   // fast kernels: every plan with enough scratch memory (staged), unsplit plans without; else the integer kernel
   const bool direct_ok = mmb::fast_supports(p, nfma);
   const bool staged_ok = mmb::staged_supports(p, nfma) && workspace &&
-                         workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S) &&
+                         workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S, false) &&
                          !(reinterpret_cast<uintptr_t>(workspace) & 127);
   if (kernel == MMB200_KERNEL_FAST && !direct_ok && !staged_ok) return MMB200_ERR_UNSUPPORTED;
   if (a_hp && (!staged_ok || kernel == MMB200_KERNEL_INTEGER)) return MMB200_ERR_UNSUPPORTED;   // only the pre-decode pass quantises
@@ -156,8 +156,8 @@ int mmb200_scaled_mm(const void* A, int64_t lda, int fmt_a, const void* B, int64
              scale_result, 1, 1, kernel, stream);
 }
 
-size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K, 1); }
-size_t mmb200_workspace_bytes_split(int M, int N, int K, int S) { return mmb::staged_workspace_bytes(M, N, K, S); }
+size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K, 1, false); }
+size_t mmb200_workspace_bytes_split(int M, int N, int K, int S) { return mmb::staged_workspace_bytes(M, N, K, S, true); }
 
 int mmb200_scaled_mm_ws(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
                         int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,

@@ -17,6 +17,7 @@
 namespace mmb {
 
 constexpr uint32_t CANON_NAN32 = 0x7FFFFFFFu;
+#define MMB200_MAX_SLICES 32
 
 // Everything a kernel needs; passed by value (__grid_constant__).
 struct Params {
@@ -55,6 +56,15 @@ struct Params {
   int seq_len;
   float* ws_tot;
   float* ws_slot;
+  // K-sliced execution of plans with few output tiles (chains are independent of one another): slice y of the grid
+  // walks the sequence entries [slice_start[y], slice_start[y + 1]) and stores its chain results, chain_base[y] onward,
+  // into ws_chains [tile][chain][output of the thread][thread]; a second kernel adds them in the plan's order
+  int slices;
+  int n_chains;
+  int plan_group;
+  int slice_start[MMB200_MAX_SLICES + 1];
+  int chain_base[MMB200_MAX_SLICES + 1];
+  float* ws_chains;
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -193,7 +203,7 @@ bool fast_supports(const Params& p, int nfma);
 // Staged fast kernel: scratch bytes it needs for a shape, and the launch (pre-decode of both operands, then the GEMM).
 // `launches` is increased by the number of kernels launched.
 bool staged_supports(const Params& p, int nfma);            // like fast_supports, any plan
-size_t staged_workspace_bytes(int M, int N, int K, int S = 1);
+size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices);
 cudaError_t launch_staged(const Params& p, int nfma, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                           int* launches);
 

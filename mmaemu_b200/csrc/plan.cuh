@@ -129,4 +129,35 @@ MMB_PLAN_HD int plan_sequence(const Plan& plan, int K, uint32_t* out) {
   return n;
 }
 
+// K slices of a tile sequence (host side of the sliced staged kernels). An entry "emits" when a chain is complete after
+// it: a chain end under slow accumulation (group != 0), else the end of a split that has tiles. plan_chains counts the
+// chains; plan_slices cuts the sequence into `slices` contiguous ranges of whole chains, as equal in chains as possible
+// (slices <= chains): slice y covers entries [slice_start[y], slice_start[y + 1]) and its first chain is chain_base[y].
+// Entries after the last chain (empty splits) belong to the last slice.
+MMB_PLAN_HD bool seq_emits(uint32_t entry, int group) {
+  return group ? (entry & SEQ_CHAIN_END) != 0 : ((entry & SEQ_SPLIT_END) && !(entry & SEQ_EMPTY));
+}
+MMB_PLAN_HD int plan_chains(const uint32_t* seq, int n, int group) {
+  int chains = 0;
+  for (int i = 0; i < n; ++i) chains += seq_emits(seq[i], group) ? 1 : 0;
+  return chains;
+}
+MMB_PLAN_HD void plan_slices(const uint32_t* seq, int n, int group, int chains, int slices, int* slice_start,
+                             int* chain_base) {
+  int y = 0, c = 0;
+  slice_start[0] = 0;
+  chain_base[0] = 0;
+  for (int i = 0; i < n && y + 1 < slices; ++i) {
+    if (!seq_emits(seq[i], group)) continue;
+    ++c;
+    if (c == (int)((long long)(y + 1) * chains / slices)) {   // chain c - 1 was the last one of slice y
+      ++y;
+      slice_start[y] = i + 1;
+      chain_base[y] = c;
+    }
+  }
+  slice_start[slices] = n;
+  chain_base[slices] = chains;
+}
+
 }  // namespace mmb

@@ -171,6 +171,9 @@ def test_launch_accounting():
     assert _lib.launch_count() == n0 + 8              # split plan: pre-decode x 2, the tile order, the GEMM kernel
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200-direct")
     assert _lib.launch_count() == n0 + 9              # without scratch memory split plans run on the integer kernel
+    a, b, ta, tb = operands(16, 16, 512, seed=8)
+    mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
+    assert _lib.launch_count() == n0 + 14             # few tiles, 4 chains: pre-decode x 2, tile order, K slices, combine
 
 
 def test_call_is_capturable_in_a_cuda_graph():

@@ -19,7 +19,7 @@ import golden_cases as G
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
-KERNELS = ("integer", "auto", "staged")     # "staged": automatic choice with scratch memory (tests/gpu_runner.py)
+KERNELS = ("integer", "auto", "staged", "staged-whole")     # "staged*": with scratch memory (tests/gpu_runner.py)
 
 
 @pytest.fixture(scope="module")

@@ -104,6 +104,31 @@ def test_sequence_reproduces_the_plan(lib, S, scheme, fast):
         assert np.array_equal(got, want), (K, S, scheme, fast)
 
 
+@pytest.mark.parametrize("fast", (True, False), ids=("fast", "slow"))
+@pytest.mark.parametrize("S,scheme", [(1, "none")] + CASES, ids=lambda v: str(v))
+def test_k_slices_are_whole_chains(lib, S, scheme, fast):
+    """The cut of the sequence into K slices: contiguous, covering, every slice with its share of whole chains."""
+    lib.plan_slices_host.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 2
+    lib.plan_slices_host.restype = ctypes.c_int
+    for K in (208, 1024, 4112, 32768):
+        seq = sequence(lib, K, fast, S, scheme)
+        slow = not fast
+        emits = [bool(int(e) & CHAIN_END) if slow else bool(int(e) & SPLIT_END and not int(e) & EMPTY) for e in seq]
+        chains = sum(emits)
+        for slices in sorted({1, 2, 3, 9, 32, chains} & set(range(1, chains + 1))):
+            start = np.full(slices + 1, -1, np.int32)
+            base = np.full(slices + 1, -1, np.int32)
+            assert lib.plan_slices_host(K, int(fast), S, SCHEME[scheme], slices, start.ctypes.data, base.ctypes.data) == chains
+            assert start[0] == 0 and start[-1] == len(seq) and base[0] == 0 and base[-1] == chains
+            assert (np.diff(start) > 0).all()
+            per = np.diff(base)
+            assert per.min() >= 1 and per.max() - per.min() <= 1
+            for y in range(slices):
+                assert sum(emits[start[y]:start[y + 1]]) == per[y]
+                if y + 1 < slices:
+                    assert emits[start[y + 1] - 1]                    # a slice ends right after a chain's last entry
+
+
 def test_capacity_is_reported(lib):
     buf = np.zeros(4, np.uint32)
     assert lib.plan_sequence_host(4096, 1, 3, SCHEME["contiguous"], buf.ctypes.data, 4) == -128
