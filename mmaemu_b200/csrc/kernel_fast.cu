@@ -669,6 +669,14 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator: the first product of a block needs no initialised registers.
+__device__ __forceinline__ void mma_bf16_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%10, %10, %10, %10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 template <int NFMA>
 __device__ __forceinline__ void block_step_tc(float (&acc)[TM][TN], const TileTC& A, const TileTC& B, int c0, int wm,
                                               int wn, int lane) {
@@ -677,12 +685,6 @@ __device__ __forceinline__ void block_step_tc(float (&acc)[TM][TN], const TileTC
   const int arow0 = 64 * wm + q * 8, bcol0 = 32 * wn + u * 8;      // permuted positions of the thread's rows / columns
   // ---- E-pass on the tensor cores: P[mi][ni] = sum over the block of 64^(ea + eb) for a 16 x 8 tile of outputs
   float P[4][4][4];
-#pragma unroll
-  for (int mi = 0; mi < 4; ++mi)
-#pragma unroll
-    for (int ni = 0; ni < 4; ++ni)
-#pragma unroll
-      for (int r = 0; r < 4; ++r) P[mi][ni][r] = 0.0f;
 #pragma unroll
   for (int k16 = c0; k16 < c0 + NFMA; k16 += 16) {
     uint32_t af[4][4], bf[2][4];
@@ -695,7 +697,10 @@ __device__ __forceinline__ void block_step_tc(float (&acc)[TM][TN], const TileTC
 #pragma unroll
     for (int mi = 0; mi < 4; ++mi)
 #pragma unroll
-      for (int ni = 0; ni < 4; ++ni) mma_bf16(P[mi][ni], af[mi], bf[ni / 2][2 * (ni % 2)], bf[ni / 2][2 * (ni % 2) + 1]);
+      for (int ni = 0; ni < 4; ++ni) {
+        if (k16 == c0) mma_bf16_first(P[mi][ni], af[mi], bf[ni / 2][2 * (ni % 2)], bf[ni / 2][2 * (ni % 2) + 1]);
+        else mma_bf16(P[mi][ni], af[mi], bf[ni / 2][2 * (ni % 2)], bf[ni / 2][2 * (ni % 2) + 1]);
+      }
   }
   // ---- block start
   uint32_t tt[TM][TN];
