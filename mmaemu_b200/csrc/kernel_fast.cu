@@ -321,7 +321,9 @@ __global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant_
   epi.store(p.D, (long long)gm * p.ldd + gn, v);
 }
 
+#if !defined(MMB_PART) || MMB_PART == 0
 __global__ void plan_sequence_kernel(Plan plan, int K, uint32_t* out) { plan_sequence(plan, K, out); }
+#endif
 
 // Non-finite patch and epilogue for the thread's 8 x 8 outputs. flag_a / flag_b: per-row classes of the tile.
 template <bool SLOW>
