@@ -94,8 +94,9 @@ int mmb200_scaled_mm(const void *A_dev, int64_t lda, int fmt_a, const void *B_de
                      void *stream);
 
 /* Same computation for HOST operands and a HOST result: copies A and B to the current device, runs the kernel, copies
- * D back and waits for it. Device staging memory comes from the stream-ordered allocator (cudaMallocAsync) and is
- * released before returning. Host buffers should be pinned for full copy speed but need not be. */
+ * D back and waits for it. Device staging memory, including the scratch memory of the staged kernels, comes from a
+ * stream-ordered memory pool of the library (cudaMallocFromPoolAsync; the pool keeps freed memory for the next call) and
+ * is returned to it before the call returns. Host buffers should be pinned for full copy speed but need not be. */
 int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void *B_host, int64_t ldb, int fmt_b,
                           void *D_host, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
                           int scheme, float scale_a, float scale_b, const float *scale_result /* host, nullable */,

@@ -1,6 +1,7 @@
 // Host side of the C ABI (include/mmaemu_b200.h): argument checks, kernel choice, launches. No allocation except in
 // mmb200_scaled_mm_host, which stages host operands through the stream-ordered allocator.
 #include <atomic>
+#include <mutex>
 #include <cstring>
 
 #include "common.cuh"
@@ -98,6 +99,33 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   if (err != cudaSuccess) return cuda_fail(err);
   g_launches.fetch_add(launches, std::memory_order_relaxed);
   return MMB200_OK;
+}
+
+// Staging memory of the host-buffer entry point: a memory pool of this library per device that keeps what it has
+// allocated (release threshold at its maximum), so that repeated calls do not return the memory to the driver at
+// every synchronisation and map it again.
+cudaError_t staging_pool(cudaMemPool_t* pool) {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    err = cudaMemPoolCreate(&pools[dev], &props);
+    if (err != cudaSuccess) { pools[dev] = nullptr; return err; }
+    unsigned long long keep = ~0ull;
+    err = cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep);
+    if (err != cudaSuccess) return err;
+  }
+  *pool = pools[dev];
+  return cudaSuccess;
 }
 
 size_t out_size(int out_dtype) {
@@ -199,8 +227,15 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
   const size_t a_bytes = (size_t)M * kpad, b_bytes = (size_t)N * kpad, d_bytes = (size_t)M * N * es;
   uint8_t* buf = nullptr;
   const size_t a_off = 0, b_off = (a_bytes + 255) / 256 * 256, d_off = b_off + (b_bytes + 255) / 256 * 256;
-  const size_t s_off = d_off + (d_bytes + 255) / 256 * 256, total = s_off + 256;
-  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&buf), total, st);
+  const size_t s_off = d_off + (d_bytes + 255) / 256 * 256, w_off = s_off + 256;
+  // scratch memory for the staged kernels, when the request can use them
+  const size_t w_bytes = (K > 0 && K % 16 == 0 && S >= 1 && S <= MMB200_MAX_SPLITS && kernel != MMB200_KERNEL_INTEGER)
+                             ? mmb::staged_workspace_bytes(M, N, K, S, true) : 0;
+  const size_t total = w_off + w_bytes;
+  cudaMemPool_t pool = nullptr;
+  cudaError_t err = staging_pool(&pool);
+  if (err != cudaSuccess) return cuda_fail(err);
+  err = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&buf), total, pool, st);
   if (err != cudaSuccess) return cuda_fail(err);
   int rc = MMB200_OK;
   float scales[3] = {scale_a, scale_b, scale_result ? *scale_result : 1.0f};
@@ -218,9 +253,9 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
     err = cudaMemcpyAsync(buf + s_off, scales, sizeof(scales), cudaMemcpyHostToDevice, st);
     if (err != cudaSuccess) break;
     const float* sdev = reinterpret_cast<const float*>(buf + s_off);
-    rc = mmb200_scaled_mm(buf + a_off, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, buf + d_off, N,
-                          out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1, scale_result ? sdev + 2 : nullptr,
-                          kernel, stream);
+    rc = mmb200_scaled_mm_ws(buf + a_off, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, buf + d_off, N,
+                             out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1,
+                             scale_result ? sdev + 2 : nullptr, kernel, w_bytes ? buf + w_off : nullptr, w_bytes, stream);
     if (rc != MMB200_OK) break;
     err = cudaMemcpy2DAsync(D, (size_t)ldd * es, buf + d_off, (size_t)N * es, (size_t)N * es, (size_t)M,
                             cudaMemcpyDeviceToHost, st);
