@@ -322,7 +322,9 @@ __global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant_
 }
 
 #if !defined(MMB_PART) || MMB_PART == 0
-__global__ void plan_sequence_kernel(Plan plan, int K, uint32_t* out) { plan_sequence(plan, K, out); }
+__global__ void plan_sequence_kernel(Plan plan, int K, uint32_t* out) {
+  plan_sequence(plan, K, out, (int)threadIdx.x, (int)blockDim.x);
+}
 #endif
 
 // Non-finite patch and epilogue for the thread's 8 x 8 outputs. flag_a / flag_b: per-row classes of the tile.
@@ -1052,7 +1054,7 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
     p.ws_tot = reinterpret_cast<float*>(base + w.tot);
     p.ws_slot = reinterpret_cast<float*>(base + w.slot);
     p.ws_chains = reinterpret_cast<float*>(base + w.chains);
-    plan_sequence_kernel<<<1, 1, 0, stream>>>(plan, p.K, reinterpret_cast<uint32_t*>(base + w.seq));
+    plan_sequence_kernel<<<1, THREADS, 0, stream>>>(plan, p.K, reinterpret_cast<uint32_t*>(base + w.seq));
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     *launches += 1;

@@ -99,32 +99,41 @@ MMB_PLAN_HD void split_order(const Plan& p, int step, int& s, int& role) {
 // the number of entries; out == nullptr only counts.
 constexpr uint32_t SEQ_TILE_MASK = 0xFFFFFu, SEQ_CHAIN_END = 1u << 20, SEQ_SPLIT_END = 1u << 21, SEQ_EMPTY = 1u << 22;
 constexpr int SEQ_ROLE_SHIFT = 24, SEQ_KT = 32;
-MMB_PLAN_HD int plan_sequence(const Plan& plan, int K, uint32_t* out) {
+MMB_PLAN_HD int plan_sequence(const Plan& plan, int K, uint32_t* out, int lane = 0, int lanes = 1) {
+  // Closed form per split, so that `lanes` workers (threads of the kernel that writes the sequence) can fill it
+  // together: worker `lane` writes the entries of every lanes-th own tile of each split. Only the last tile of K can be
+  // narrower than W, so the j-th own tile of a split starts j * (W / 32) entries after the split's first entry.
+  const int per = plan.W / SEQ_KT;
   int n = 0;
   for (int step = 0; step < plan.S; ++step) {
     int s, role, first, end, tstep;
     split_order(plan, step, s, role);
     split_tiles(plan, s, first, end, tstep);
-    int cnt = 0, last = -1;
-    for (int t = first; t < end; t += tstep) {
-      const long long kbeg = (long long)t * plan.W;
-      const long long kend = kbeg + plan.W < (long long)K ? kbeg + plan.W : (long long)K;
-      for (long long k0 = kbeg; k0 < kend; k0 += SEQ_KT) {
-        if (out) out[n] = (uint32_t)(k0 / SEQ_KT);
-        last = n++;
-      }
-      if (plan.group && ++cnt == plan.group) {
-        if (out) out[last] |= SEQ_CHAIN_END;
-        cnt = 0;
+    const uint32_t split_end = SEQ_SPLIT_END | ((uint32_t)role << SEQ_ROLE_SHIFT);
+    const int nt = first < end ? (end - 1 - first) / tstep + 1 : 0;
+    if (nt == 0) {
+      if (out && lane == 0) out[n] = SEQ_EMPTY | split_end;
+      n += 1;
+      continue;
+    }
+    const long long last_beg = (long long)(first + (nt - 1) * tstep) * plan.W;
+    const long long last_end = last_beg + plan.W < (long long)K ? last_beg + plan.W : (long long)K;
+    const int last_sub = (int)((last_end - last_beg + SEQ_KT - 1) / SEQ_KT);
+    if (out) {
+      for (int j = lane; j < nt; j += lanes) {
+        const long long k32 = (long long)(first + j * tstep) * per;
+        const int ns = j == nt - 1 ? last_sub : per;
+        for (int sub = 0; sub < ns; ++sub) {
+          uint32_t e = (uint32_t)(k32 + sub);
+          if (sub == ns - 1) {
+            if (plan.group && (j + 1) % plan.group == 0) e |= SEQ_CHAIN_END;
+            if (j == nt - 1) e |= split_end | ((plan.group && nt % plan.group) ? SEQ_CHAIN_END : 0u);
+          }
+          out[n + j * per + sub] = e;
+        }
       }
     }
-    if (last < 0) {
-      if (out) out[n] = SEQ_EMPTY;
-      last = n++;
-    } else if (plan.group && cnt) {
-      if (out) out[last] |= SEQ_CHAIN_END;
-    }
-    if (out) out[last] |= SEQ_SPLIT_END | ((uint32_t)role << SEQ_ROLE_SHIFT);
+    n += (nt - 1) * per + last_sub;
   }
   return n;
 }

@@ -22,3 +22,13 @@ extern "C" int plan_slices_host(int K, int fast, int S, int scheme, int slices, 
   delete[] seq;
   return chains;
 }
+
+// The sequence written by `lanes` workers one after the other, as the threads of the device kernel write it together.
+extern "C" int plan_sequence_lanes_host(int K, int fast, int S, int scheme, uint32_t* out, int capacity, int lanes) {
+  const mmb::Plan plan = mmb::make_plan(K, fast, S, scheme);
+  const int n = mmb::plan_sequence(plan, K, nullptr);
+  if (n > capacity) return -n;
+  for (int lane = 0; lane < lanes; ++lane)
+    if (mmb::plan_sequence(plan, K, out, lane, lanes) != n) return 0;
+  return n;
+}

@@ -129,6 +129,20 @@ def test_k_slices_are_whole_chains(lib, S, scheme, fast):
                     assert emits[start[y + 1] - 1]                    # a slice ends right after a chain's last entry
 
 
+@pytest.mark.parametrize("fast", (True, False), ids=("fast", "slow"))
+def test_workers_write_the_same_sequence(lib, fast):
+    """The device kernel fills the sequence with 256 threads; any number of workers must give the serial result."""
+    lib.plan_sequence_lanes_host.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    lib.plan_sequence_lanes_host.restype = ctypes.c_int
+    for S, scheme in [(1, "none")] + CASES:
+        for K in (64, 208, 1936, 4112, 65552):
+            want = sequence(lib, K, fast, S, scheme)
+            for lanes in (3, 256):
+                buf = np.full(want.size + 4, 0xFFFFFFFF, np.uint32)
+                n = lib.plan_sequence_lanes_host(K, int(fast), S, SCHEME[scheme], buf.ctypes.data, buf.size, lanes)
+                assert n == want.size and np.array_equal(buf[:n], want) and (buf[n:] == 0xFFFFFFFF).all()
+
+
 def test_capacity_is_reported(lib):
     buf = np.zeros(4, np.uint32)
     assert lib.plan_sequence_host(4096, 1, 3, SCHEME["contiguous"], buf.ctypes.data, 4) == -128
