@@ -61,7 +61,7 @@ extern "C" {
 /* kernel families */
 #define MMB200_KERNEL_AUTO 0     /* the fastest kernel that serves the request */
 #define MMB200_KERNEL_INTEGER 1  /* pure-integer block model: every format pair and plan */
-#define MMB200_KERNEL_FAST 2     /* fp32 round-toward-zero FMA chain with integer corrections (see DESIGN.md) */
+#define MMB200_KERNEL_FAST 2     /* fp32 round-toward-zero FMA chain with integer corrections */
 
 #define MMB200_MAX_SPLITS 64
 

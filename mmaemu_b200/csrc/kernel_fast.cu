@@ -286,18 +286,22 @@ __global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant_
   const float* src = p.ws_chains + (size_t)blockIdx.x * p.n_chains * (TM * TN * THREADS) + (size_t)idx * THREADS + tid;
   const bool slow = p.plan_group != 0;
   float tot = 0.0f, slot = 0.0f, part = 0.0f, last = 0.0f;
-  // the next two chain results are always in flight: the loads do not depend on the additions
+  // the next four chain results are always in flight: the loads do not depend on the additions
   constexpr size_t STRIDE = (size_t)TM * TN * THREADS;
-  float ahead0 = src[0], ahead1 = p.n_chains > 1 ? src[STRIDE] : 0.0f;
+  constexpr int AHEAD = 4;
+  float ahead[AHEAD];
+#pragma unroll
+  for (int q = 0; q < AHEAD; ++q) ahead[q] = q < p.n_chains ? src[(size_t)q * STRIDE] : 0.0f;
   int chain = 0;
 #pragma unroll 1
   for (int e = 0; e < p.seq_len; ++e) {
     const uint32_t entry = __ldg(p.ws_seq + e);
     if (seq_emits(entry, slow ? 1 : 0)) {
-      last = ahead0;
-      ahead0 = ahead1;
+      last = ahead[0];
+#pragma unroll
+      for (int q = 0; q + 1 < AHEAD; ++q) ahead[q] = ahead[q + 1];
       ++chain;
-      ahead1 = chain + 1 < p.n_chains ? src[(size_t)(chain + 1) * STRIDE] : 0.0f;
+      ahead[AHEAD - 1] = chain + AHEAD - 1 < p.n_chains ? src[(size_t)(chain + AHEAD - 1) * STRIDE] : 0.0f;
       if (slow) part = __fadd_rn(part, last);
     }
     if (entry & SEQ_SPLIT_END) {

@@ -15,6 +15,7 @@ import argparse
 import hashlib
 import io
 import json
+import os
 from pathlib import Path
 
 import numpy as np
@@ -58,7 +59,7 @@ def convert(src: Path, table_id: str) -> None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MMAEMU_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference")))
     a = ap.parse_args()
     for t in TABLES:
         convert(Path(a.reference) / "mmaemu" / "platform" / "data", t)

@@ -12,7 +12,7 @@ tests/data/hw_mini, the 124 H100 PCIe live calls of tests/data/h100_mini (sha256
 recorded epilogue ties and hardware extracts of tests/data/epilogue, the 50,000 MATLAB-toolbox instruction vectors, the
 hard-coded hardware bytes in tests/test_api.py, and the unit tests of the plan layouts and reduction orders.
 
-usage:  python oracle/pin_against_reference.py [--reference /root/reference] [pytest args]
+usage:  python oracle/pin_against_reference.py [--reference <checkout of astding/mmaemu>] [pytest args]
 Prints how many calls were served by the oracle and how many fell back to the reference's own code (custom presets,
 late-c presets, non-finite instruction-level operands), then pytest's summary. Exit code = pytest's.
 """
@@ -119,7 +119,7 @@ class OraclePatch:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--reference", default=os.environ.get("MMAEMU_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("MMAEMU_REFERENCE", str(Path(__file__).resolve().parents[2] / "reference")))
     ap.add_argument("--tests", nargs="*", default=DEFAULT_TESTS)
     args, rest = ap.parse_known_args(argv)
     ref = Path(args.reference)

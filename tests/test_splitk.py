@@ -5,6 +5,7 @@ import os
 import random
 import sys
 import warnings
+from pathlib import Path
 
 import pytest
 import torch
@@ -92,7 +93,7 @@ def test_unverified_combination_warns_once():
         resolve(64, 64, 4096, profile="hopper", splitk=(2, "serial"), dry=True)           # dry: every time
 
 
-REFERENCE = os.environ.get("MMAEMU_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("MMAEMU_REFERENCE", str(Path(__file__).resolve().parents[2] / "reference"))
 
 
 @pytest.mark.skipif(not os.path.isfile(os.path.join(REFERENCE, "mmaemu", "platform", "splitk_table.py")),
