@@ -487,6 +487,7 @@ struct Stage {
 struct SmemStaged {
   Stage stage[2];
   unsigned long long full[2];              // mbarriers: "the stage's two copies have landed"
+  unsigned long long empty[2];             // mbarriers: "every warp is done reading the stage" (one arrival per warp)
   float part[TM * TN][THREADS];            // slow accumulation only
 };
 constexpr size_t SMEM_STAGED_FAST = offsetof(SmemStaged, part), SMEM_STAGED_SLOW = sizeof(SmemStaged);
@@ -500,6 +501,9 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 // Bounded wait for the phase with the given parity. Returns false if the bound ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
@@ -546,6 +550,8 @@ __global__ void __launch_bounds__(THREADS, 1) staged_kernel(const __grid_constan
   if (tid == 0) {
     mbar_init(&sm.full[0], 1);
     mbar_init(&sm.full[1], 1);
+    mbar_init(&sm.empty[0], THREADS / 32);
+    mbar_init(&sm.empty[1], THREADS / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -579,11 +585,21 @@ __global__ void __launch_bounds__(THREADS, 1) staged_kernel(const __grid_constan
         after_tile<SLOW, MODE>(p, acc, sm.part, t, entry, tid, chain);
       }
     }
-    __syncthreads();                       // every thread is done with stage t % 2 (or has given up)
-    if (tid == 0 && ok && t + 2 < T) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // order the generic reads before the async writes
-      issue(t + 2);
+    // Release of stage t % 2 without a barrier of the whole CTA: every warp arrives once it has read the stage (or has
+    // given up); only the issuing thread waits for all of them, so the other warps may run up to one k-tile ahead.
+    __syncwarp();
+    if (tid % 32 == 0) mbar_arrive(&sm.empty[t & 1]);
+    if (tid == 0 && t + 2 < T) {
+      if (ok && !mbar_wait(&sm.empty[t & 1], (t >> 1) & 1)) {
+        ok = false;
+        if (p.status) atomicExch(p.status, 1);
+      }
+      if (ok) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // order the generic reads before the async writes
+        issue(t + 2);
+      }
     }
+    if (tid < 32) ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;   // the issuing thread's warp follows it
   }
   if (!ok || SLICED) return;                 // a slice has stored its chains; the combine kernel writes the output
   if (!PLAN && (!SLOW || (T % 4) != 0)) chain_end<SLOW>(acc, sm.part, tid);
@@ -661,6 +677,7 @@ struct StageTC {
 struct SmemStagedTC {
   StageTC stage[2];
   unsigned long long full[2];
+  unsigned long long empty[2];
   float part[TM * TN][THREADS];
 };
 constexpr size_t SMEM_TC_FAST = offsetof(SmemStagedTC, part), SMEM_TC_SLOW = sizeof(SmemStagedTC);
@@ -749,6 +766,8 @@ __global__ void __launch_bounds__(THREADS, 1) staged_tc_kernel(const __grid_cons
   if (tid == 0) {
     mbar_init(&sm.full[0], 1);
     mbar_init(&sm.full[1], 1);
+    mbar_init(&sm.empty[0], THREADS / 32);
+    mbar_init(&sm.empty[1], THREADS / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -782,11 +801,21 @@ __global__ void __launch_bounds__(THREADS, 1) staged_tc_kernel(const __grid_cons
         after_tile<SLOW, MODE>(p, acc, sm.part, t, entry, tid, chain);
       }
     }
-    __syncthreads();
-    if (tid == 0 && ok && t + 2 < T) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue(t + 2);
+    // Release of stage t % 2 without a barrier of the whole CTA: every warp arrives once it has read the stage (or has
+    // given up); only the issuing thread waits for all of them, so the other warps may run up to one k-tile ahead.
+    __syncwarp();
+    if (tid % 32 == 0) mbar_arrive(&sm.empty[t & 1]);
+    if (tid == 0 && t + 2 < T) {
+      if (ok && !mbar_wait(&sm.empty[t & 1], (t >> 1) & 1)) {
+        ok = false;
+        if (p.status) atomicExch(p.status, 1);
+      }
+      if (ok) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // order the generic reads before the async writes
+        issue(t + 2);
+      }
     }
+    if (tid < 32) ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;   // the issuing thread's warp follows it
   }
   if (!ok || SLICED) return;                 // a slice has stored its chains; the combine kernel writes the output
   if (!PLAN && (!SLOW || (T % 4) != 0)) chain_end<SLOW>(acc, sm.part, tid);
