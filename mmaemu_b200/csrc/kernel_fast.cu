@@ -15,8 +15,9 @@
 //                  tile (no scratch memory; each CTA decodes its own tiles);
 //   staged_kernel  reads tiles that predecode_kernel decoded ONCE into scratch memory in exactly the shared-memory
 //                  layout, with two bulk asynchronous copies (TMA engine, cp.async.bulk) per k-tile into a two-stage
-//                  ring guarded by mbarriers -- no decode instructions, no register staging and one barrier per k-tile
-//                  in the main loop. Every wait on an mbarrier is bounded; a wait that gives up records a status word.
+//                  ring guarded by mbarriers ("full": the copies have landed; "empty": every warp has read the stage)
+//                  -- no decode instructions, no register staging and no barrier of the whole CTA in the main loop.
+//                  Every wait on an mbarrier is bounded; a wait that gives up records a status word.
 // Non-finite codes are decoded as +0 and flagged per row / column; flagged outputs get their IEEE value in the
 // epilogue. Slow accumulation keeps the running fp32 sum of chain results in shared memory.
 #include <cstdlib>
