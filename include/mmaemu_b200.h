@@ -4,8 +4,9 @@
  * Every function is a host function of libmmaemu_b200.so. Pointers named *_dev are device pointers owned by the
  * caller; nothing is allocated internally unless a function says so. All launches are asynchronous on the given
  * cudaStream_t (passed as void*; NULL = the legacy default stream). Functions return MMB200_OK (0) or a negative
- * status, never throw and never abort. The library holds no mutable global state apart from per-device function
- * attributes that are set once.
+ * status, never throw and never abort. Mutable state of the library: per-device function attributes that are set once;
+ * the per-device memory pool of mmb200_scaled_mm_host; the fixed scratch array of mmb200_scaled_mm_static with its
+ * cached per-device address; the launch counter; the process-wide test hooks of mmb200_test_hooks.
  *
  * Operands are FP8 code bytes: A is [M, K] row-major with leading dimension lda (bytes), B is [N, K] row-major with
  * leading dimension ldb -- that is mat2.t() of torch._scaled_mm's column-major [K, N] operand.
@@ -31,7 +32,7 @@
 extern "C" {
 #endif
 
-#define MMB200_ABI_VERSION 3
+#define MMB200_ABI_VERSION 4
 
 /* status codes */
 #define MMB200_OK 0
@@ -40,6 +41,7 @@ extern "C" {
 #define MMB200_ERR_ARCH (-3)          /* the current device is not sm_100 (the fatbin holds sm_100a code only) */
 #define MMB200_ERR_LAUNCH (-4)        /* the CUDA runtime refused the launch or a copy (see mmb200_last_cuda_error) */
 #define MMB200_ERR_TOO_LARGE (-5)     /* a size is beyond a documented limit */
+#define MMB200_ERR_TIMEOUT (-6)       /* a bounded wait inside a kernel ran out; the output was not written */
 
 /* FP8 operand formats (mmaemu/formats.py:14-19) */
 #define MMB200_FMT_E4M3 0
@@ -125,6 +127,23 @@ int mmb200_scaled_mm_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B
 int mmb200_accumulate_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
                          float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
                          int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* Bounded waits and their status word. The scratch-memory kernels wait for their bulk copies on mbarriers with a bound
+ * (about four seconds); a wait that runs out makes the kernel record 1 in a status word inside the scratch memory, skip
+ * the output (D keeps its previous contents) and return, instead of spinning forever. Launches are asynchronous, so the
+ * word is read after the stream has drained: mmb200_workspace_status synchronises `stream`, reads the word of the call
+ * that last used `workspace_dev` with this shape and split count, and returns MMB200_OK or MMB200_ERR_TIMEOUT;
+ * mmb200_workspace_status_offset gives the byte offset of the int32 word for callers that read it themselves
+ * (mmb200_scaled_mm_host checks it before copying D back and returns MMB200_ERR_TIMEOUT). The reference has no
+ * counterpart: its kernels hold no waits (mmaemu/backends/cuda/csrc/h4.cu:289-303 synchronises with barriers only). */
+size_t mmb200_workspace_status_offset(int M, int N, int K, int S);
+int mmb200_workspace_status(const void *workspace_dev, int M, int N, int K, int S, void *stream);
+/* The same for the fixed scratch array of mmb200_scaled_mm_static on the current device. */
+int mmb200_scaled_mm_static_status(int M, int N, int K, void *stream);
+/* Test hook, process-wide: every later scratch-memory launch bounds its waits by `wait_polls` polls (<= 0: the
+ * default) and announces `announce_extra_bytes` more bytes per stage to the mbarrier than it copies (<= 0: none), so
+ * that the wait runs out without anything faulting. For the tests of the status word only. */
+void mmb200_test_hooks(int wait_polls, int announce_extra_bytes);
 
 /* Quantise prologue fused into the staged path: the activations X [M, K] (MMB200_HP_F32 or MMB200_HP_BF16, row stride
  * ldx elements, 16-byte aligned rows) are multiplied by *quant_scale_dev, clamped to +-448 and rounded to E4M3 (nearest

@@ -12,18 +12,19 @@ from pathlib import Path
 from .errors import BackendUnavailableError
 
 LIB_PATH = Path(__file__).resolve().parent / "libmmaemu_b200.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 FMT_CODES = {"e4m3": 0, "e5m2": 1}
 OUT_CODES = {"float32": 0, "bfloat16": 1, "float16": 2, "float8_e4m3fn": 3, "float8_e5m2": 4}
 SCHEME_CODES = {"none": 0, "serial": 1, "pairwise": 2, "contiguous": 3}
 KERNEL_CODES = {"auto": 0, "integer": 1, "fast": 2}
-OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_ARCH, ERR_LAUNCH, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_ARCH, ERR_LAUNCH, ERR_TOO_LARGE, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
 
 EXPORTS = ("mmb200_abi_version", "mmb200_status_string", "mmb200_last_cuda_error", "mmb200_device_supported",
            "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_kernel_for",
            "mmb200_launch_count", "mmb200_workspace_bytes", "mmb200_workspace_bytes_split", "mmb200_scaled_mm_ws", "mmb200_accumulate_ws",
-           "mmb200_scaled_mm_static", "mmb200_quantize_scaled_mm_ws")
+           "mmb200_scaled_mm_static", "mmb200_quantize_scaled_mm_ws", "mmb200_workspace_status_offset",
+           "mmb200_workspace_status", "mmb200_scaled_mm_static_status", "mmb200_test_hooks")
 
 _lock = threading.Lock()
 _lib = None
@@ -85,6 +86,14 @@ def load():
         L.mmb200_accumulate_ws.restype = ci
         L.mmb200_scaled_mm_static.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, vp, vp, vp, vp]
         L.mmb200_scaled_mm_static.restype = ci
+        L.mmb200_workspace_status_offset.argtypes = [ci, ci, ci, ci]
+        L.mmb200_workspace_status_offset.restype = ctypes.c_size_t
+        L.mmb200_workspace_status.argtypes = [vp, ci, ci, ci, ci, vp]
+        L.mmb200_workspace_status.restype = ci
+        L.mmb200_scaled_mm_static_status.argtypes = [ci, ci, ci, vp]
+        L.mmb200_scaled_mm_static_status.restype = ci
+        L.mmb200_test_hooks.argtypes = [ci, ci]
+        L.mmb200_test_hooks.restype = None
         L.mmb200_kernel_for.argtypes = [vp, i64, vp, i64, ci, ci, ci]
         L.mmb200_kernel_for.restype = ci
         L.mmb200_launch_count.argtypes = []

@@ -326,6 +326,11 @@ def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -
                                    c.preset.nfma, int(fast), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb, pr,
                                    _kernel_code(c.kernel), ws_ptr, ws_bytes, _stream_ptr(dev))
     _lib.check("mmb200_scaled_mm_ws", rc)
+    if ws is not None and os.environ.get("MMAEMU_B200_CHECK_STATUS", "0") == "1":
+        # opt-in: wait for the call and read the status word of its bounded waits (a host synchronisation per call)
+        with torch.cuda.device(dev):
+            _lib.check("mmb200_workspace_status", L.mmb200_workspace_status(ws_ptr, c.M, c.N, c.K, c.decision.S,
+                                                                            _stream_ptr(dev)))
     del keep_a, keep_b, keep_r, ws
     return y
 

@@ -118,16 +118,20 @@ BACKEND = B200Backend()
 
 def install_into_reference():
     """Make an importable `mmaemu` package select this backend: backend='cuda:b200' always, and 'auto' / 'cuda' when
-    the request's device is sm_100. Everything else falls through to the reference's own selection rules. Returns the
-    patched registry module. Idempotent."""
+    the request's device is sm_100. Everything else falls through to the reference's own selection rules
+    (mmaemu/backends/registry.py:194-267). `mmaemu.backends_status()` and `mmaemu.explain()` report the backend too.
+    Errors are raised with the reference's own exception classes. Returns the patched registry module. Idempotent."""
     import importlib
     registry = importlib.import_module("mmaemu.backends.registry")
     if getattr(registry, "_mmaemu_b200_installed", False):
         return registry
-    original = registry.select
+    ref_errors = importlib.import_module("mmaemu.errors")
+    backends = importlib.import_module("mmaemu.backends")
+    original_select, original_explain, original_status = registry.select, registry.explain_selection, registry.status
     by_name = {NAME: BACKEND, f"{NAME}-integer": B200Backend("integer"), f"{NAME}-fast": B200Backend("fast")}
 
-    def select(req, backend="auto"):
+    def _choose(req, backend):
+        """The B200 backend object for this request and backend name, or None to fall through."""
         import os
         name = backend
         if name == "auto":
@@ -136,15 +140,47 @@ def install_into_reference():
             be = by_name[name]
             why = be.supports(req)
             if why is not None:
-                raise BackendUnavailableError(f"backend {name!r} cannot serve this call: {why}")
+                raise ref_errors.BackendUnavailableError(f"backend {name!r} cannot serve this call: {why}")
             return be
         if name in ("auto", "cuda") and BACKEND.supports(req) is None:
             return BACKEND
-        return original(req, backend)
+        return None
 
-    registry.select = select
+    def select(req, backend="auto"):
+        be = _choose(req, backend)
+        return be if be is not None else original_select(req, backend)
+
+    def explain_selection(req, backend="auto"):
+        be = _choose(req, backend)
+        return (be, []) if be is not None else original_explain(req, backend)
+
+    def status(device=None):
+        import torch
+        out = original_status(device)
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        dev = torch.device(device)
+        req = backends.ChainRequest(device=dev, fmt_a="e4m3", fmt_b="e4m3", preset="hopper")
+        why = BACKEND.supports(req)
+        entry = backends.BackendStatus(name=NAME, available=why is None, source="precompiled sm_100a" if why is None else None,
+                                       validated_here=why is None, reason=why or "")
+        return {NAME: entry, **out}
+
+    registry.select, registry.explain_selection, registry.status = select, explain_selection, status
     registry._mmaemu_b200_installed = True
-    backends = importlib.import_module("mmaemu.backends")
+    registry._mmaemu_b200_originals = (original_select, original_explain, original_status)
     if NAME not in backends.BACKEND_NAMES:
         backends.BACKEND_NAMES = tuple(backends.BACKEND_NAMES) + tuple(by_name)
     return registry
+
+
+def uninstall_from_reference():
+    """Undo install_into_reference (tests)."""
+    import importlib
+    registry = importlib.import_module("mmaemu.backends.registry")
+    if not getattr(registry, "_mmaemu_b200_installed", False):
+        return
+    registry.select, registry.explain_selection, registry.status = registry._mmaemu_b200_originals
+    registry._mmaemu_b200_installed = False
+    backends = importlib.import_module("mmaemu.backends")
+    backends.BACKEND_NAMES = tuple(n for n in backends.BACKEND_NAMES if not n.startswith(NAME))

@@ -18,6 +18,17 @@ int cuda_fail(cudaError_t err) {
   return MMB200_ERR_LAUNCH;
 }
 
+// Status word of a staged launch, read after the stream has drained.
+int read_status(const void* workspace, int M, int N, int K, int S, cudaStream_t st) {
+  if (!workspace || M <= 0 || N <= 0 || K <= 0) return MMB200_OK;
+  int word = 0;
+  cudaError_t err = cudaMemcpyAsync(&word, static_cast<const unsigned char*>(workspace) + mmb::staged_status_offset(M, N, K, S),
+                                    sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+  if (err != cudaSuccess) return cuda_fail(err);
+  return word ? MMB200_ERR_TIMEOUT : MMB200_OK;
+}
+
 bool fmt_ok(int f) { return f == MMB200_FMT_E4M3 || f == MMB200_FMT_E5M2; }
 
 int current_device_ok() {
@@ -134,6 +145,8 @@ size_t out_size(int out_dtype) {
 
 }  // namespace
 
+int mmb::record_cuda_error(cudaError_t err) { return cuda_fail(err); }
+
 extern "C" {
 
 int mmb200_abi_version(void) { return MMB200_ABI_VERSION; }
@@ -146,6 +159,7 @@ const char* mmb200_status_string(int status) {
     case MMB200_ERR_ARCH: return "the device is not sm_100 (this library holds sm_100a kernels only)";
     case MMB200_ERR_LAUNCH: return "CUDA runtime error (see mmb200_last_cuda_error)";
     case MMB200_ERR_TOO_LARGE: return "size beyond a documented limit";
+    case MMB200_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out; the output was not written";
     default: return "unknown status";
   }
 }
@@ -183,6 +197,15 @@ int mmb200_scaled_mm(const void* A, int64_t lda, int fmt_a, const void* B, int64
   return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
              scale_result, 1, 1, kernel, stream);
 }
+
+size_t mmb200_workspace_status_offset(int M, int N, int K, int S) { return mmb::staged_status_offset(M, N, K, S); }
+
+int mmb200_workspace_status(const void* workspace, int M, int N, int K, int S, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || S < 1) return MMB200_ERR_BAD_ARG;
+  return read_status(workspace, M, N, K, S, static_cast<cudaStream_t>(stream));
+}
+
+void mmb200_test_hooks(int wait_polls, int announce_extra_bytes) { mmb::staged_test_hooks(wait_polls, announce_extra_bytes); }
 
 size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K, 1, false); }
 size_t mmb200_workspace_bytes_split(int M, int N, int K, int S) { return mmb::staged_workspace_bytes(M, N, K, S, true); }
@@ -257,6 +280,10 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
                              out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1,
                              scale_result ? sdev + 2 : nullptr, kernel, w_bytes ? buf + w_off : nullptr, w_bytes, stream);
     if (rc != MMB200_OK) break;
+    if (w_bytes) {                        // the staged kernels report a wait that ran out; D is then not copied back
+      rc = read_status(buf + w_off, M, N, K, S, st);
+      if (rc != MMB200_OK) break;
+    }
     err = cudaMemcpy2DAsync(D, (size_t)ldd * es, buf + d_off, (size_t)N * es, (size_t)N * es, (size_t)M,
                             cudaMemcpyDeviceToHost, st);
   } while (0);

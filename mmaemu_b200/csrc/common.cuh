@@ -42,6 +42,8 @@ struct Params {
   int* status;
   int k_tiles;
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
+  int wait_polls;        // bound of every wait on an mbarrier in the staged kernels, in polls of up to ~1 us each
+  int test_announce_extra;  // test hook: bytes the issuing thread announces beyond what it copies (the wait then runs out)
   // quantise prologue (staged kernels, operand A in E4M3 only): when a_hp is set, the pre-decode pass reads M x K
   // activations of a_hp_dtype (MMB200_HP_F32 / MMB200_HP_BF16, row stride ld_hp elements), forms the E4M3 codes of
   // clamp(x * *a_quant_scale, +-448), writes them to a_codes (row stride lda; A must point there too) and decodes them
@@ -206,5 +208,12 @@ bool staged_supports(const Params& p, int nfma);            // like fast_support
 size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices);
 cudaError_t launch_staged(const Params& p, int nfma, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                           int* launches);
+// Byte offset, inside the scratch memory of a staged launch, of the int32 status word (0, or 1 when a bounded wait ran
+// out and the output was not written); the same with and without K slices.
+size_t staged_status_offset(int M, int N, int K, int S);
+// Test hooks of the bounded waits (process-wide; wait_polls <= 0 and announce_extra <= 0 restore the defaults).
+void staged_test_hooks(int wait_polls, int announce_extra);
+// Text of the last CUDA runtime error seen by this thread inside the library; returns MMB200_ERR_LAUNCH.
+int record_cuda_error(cudaError_t err);
 
 }  // namespace mmb

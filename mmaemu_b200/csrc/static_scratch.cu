@@ -35,16 +35,21 @@ void* g_scratch_ptr[MAX_DEVICES] = {};
 // The array's address on the current device (looked up on first use there), or nullptr with `status` set.
 void* scratch_on_current_device(int* status) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
-    *status = MMB200_ERR_LAUNCH;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) {
+    *status = mmb::record_cuda_error(err);
+    return nullptr;
+  }
+  if (dev < 0 || dev >= MAX_DEVICES) {
+    *status = MMB200_ERR_UNSUPPORTED;          // device ordinal beyond the address cache
     return nullptr;
   }
   std::lock_guard<std::mutex> lock(g_mutex);
   if (!g_scratch_ptr[dev]) {
     void* ptr = nullptr;
-    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    err = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (err != cudaSuccess || !ptr) {
-      *status = MMB200_ERR_LAUNCH;
+      *status = mmb::record_cuda_error(err != cudaSuccess ? err : cudaErrorInvalidSymbol);
       return nullptr;
     }
     g_scratch_ptr[dev] = ptr;
@@ -59,6 +64,10 @@ extern "C" int mmb200_scaled_mm_static(const void* A, int64_t lda, int fmt_a, co
                                        const float* scale_a, const float* scale_b, const float* scale_result,
                                        void* stream) {
   if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
+  if ((fmt_a != MMB200_FMT_E4M3 && fmt_a != MMB200_FMT_E5M2) || (fmt_b != MMB200_FMT_E4M3 && fmt_b != MMB200_FMT_E5M2))
+    return MMB200_ERR_BAD_ARG;
+  if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2 || !scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
+  if (nfma != 16 && nfma != 32) return MMB200_ERR_UNSUPPORTED;
   if (M == 0 || N == 0) return MMB200_OK;
   // only requests the scratch-memory kernel serves: unsplit plan, K % 16 == 0, 16-byte aligned operands
   if (K == 0 || mmb200_kernel_for(A, lda, B, ldb, K, nfma, 1) != MMB200_KERNEL_FAST) return MMB200_ERR_UNSUPPORTED;
@@ -68,4 +77,13 @@ extern "C" int mmb200_scaled_mm_static(const void* A, int64_t lda, int fmt_a, co
   if (!scratch) return status;
   return mmb200_scaled_mm_ws(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, 1, MMB200_SCHEME_NONE,
                              scale_a, scale_b, scale_result, MMB200_KERNEL_FAST, scratch, SCRATCH_BYTES, stream);
+}
+
+extern "C" int mmb200_scaled_mm_static_status(int M, int N, int K, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
+  if (M == 0 || N == 0 || K == 0) return MMB200_OK;
+  int status = MMB200_OK;
+  void* scratch = scratch_on_current_device(&status);
+  if (!scratch) return status;
+  return mmb200_workspace_status(scratch, M, N, K, 1, stream);
 }

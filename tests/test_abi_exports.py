@@ -36,7 +36,7 @@ def test_every_declared_function_is_exported(lib):
 def test_status_codes_and_argument_checks_without_a_device(lib):
     from mmaemu_b200 import _lib
     assert lib.mmb200_abi_version() == int(re.search(r"#define MMB200_ABI_VERSION (\d+)", HEADER).group(1))
-    for code in (0, -1, -2, -3, -4, -5):
+    for code in (0, -1, -2, -3, -4, -5, -6):
         assert lib.mmb200_status_string(code).decode() not in ("", "unknown status")
     assert lib.mmb200_status_string(-99).decode() == "unknown status"
     buf = ctypes.create_string_buffer(64)
@@ -50,6 +50,18 @@ def test_status_codes_and_argument_checks_without_a_device(lib):
     assert lib.mmb200_scaled_mm(p, 16, 0, p, 16, 0, p, 1, 1, 1, 1, 16, 32, 1, 1, 0, None, None, None, 0, None) \
         == _lib.ERR_BAD_ARG                                                                            # no scales
     assert lib.mmb200_chain(p, 16, 0, p, 16, 0, p, 1, 0, 5, 16, 32, 0, None) == _lib.OK               # empty result
+    # the entry point without allocation validates before it looks at sizes or the device, as the others do
+    s = p + 32
+    assert lib.mmb200_scaled_mm_static(p, 16, 7, p, 16, 0, p, 16, 1, 0, 16, 16, 32, 1, s, s, None, None) == _lib.ERR_BAD_ARG
+    assert lib.mmb200_scaled_mm_static(p, 16, 0, p, 16, 0, p, 16, 9, 0, 16, 16, 32, 1, s, s, None, None) == _lib.ERR_BAD_ARG
+    assert lib.mmb200_scaled_mm_static(p, 16, 0, p, 16, 0, p, 16, 1, 0, 16, 16, 32, 1, None, s, None, None) == _lib.ERR_BAD_ARG
+    assert lib.mmb200_scaled_mm_static(p, 16, 0, p, 16, 0, p, 16, 1, 0, 16, 16, 32, 1, s, s, None, None) == _lib.OK
+    # the status word of the scratch-memory kernels: where it lives, and argument checks of its reader
+    off = lib.mmb200_workspace_status_offset(4096, 4096, 4096, 1)
+    assert 0 < off < lib.mmb200_workspace_bytes(4096, 4096, 4096) and off % 4 == 0
+    assert off == lib.mmb200_workspace_status_offset(4096, 4096, 4096, 4)      # a prefix shared by every layout
+    assert lib.mmb200_workspace_status(None, 16, 16, 16, 1, None) == _lib.OK    # no scratch memory: nothing to report
+    assert lib.mmb200_workspace_status(p, -1, 16, 16, 1, None) == _lib.ERR_BAD_ARG
     assert lib.mmb200_launch_count() == 0
 
 
@@ -64,3 +76,9 @@ def test_no_device_is_a_status_not_a_crash(lib):
     assert rc in (_lib.ERR_LAUNCH, _lib.ERR_ARCH)
     with pytest.raises(Exception):
         _lib.check("mmb200_chain", rc)
+    # the entry point without allocation records the CUDA error text when it cannot reach a device
+    s = p + 32
+    rc = lib.mmb200_scaled_mm_static(p, 16, 0, p, 16, 0, p, 16, 1, 16, 16, 16, 32, 1, s, s, None, None)
+    assert rc in (_lib.ERR_LAUNCH, _lib.ERR_ARCH)
+    if rc == _lib.ERR_LAUNCH:
+        assert lib.mmb200_last_cuda_error().decode() != ""

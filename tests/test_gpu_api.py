@@ -1,6 +1,8 @@
 """The Python entry points on a B200 (-m gpu): mmaemu_b200.scaled_mm / accumulate / the Backend object, bit for bit
 against the oracle, plus the behaviours the reference pins at this boundary (tests/test_api.py and
 tests/test_cuda_runtime.py of astding/mmaemu): out= handling, zero sizes, storage offsets, the current stream."""
+import ctypes
+import os
 import warnings
 
 import numpy as np
@@ -9,6 +11,7 @@ import torch
 
 import datagen
 import mmaemu_b200 as mm
+from mmaemu_b200 import _lib
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -252,3 +255,55 @@ def test_quantised_activations_argument_checks():
         mm.quantized_scaled_mm(x, 2.0, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1)
     with pytest.raises(mm.SplitKUnknownError):                      # scaled_mm's own checks apply to the produced tensor
         mm.quantized_scaled_mm(x, one, w.t(), one, one, out_dtype=torch.bfloat16, profile="hopper")
+
+
+def test_a_wait_that_runs_out_is_reported_and_nothing_is_written():
+    """The scratch-memory kernels bound every wait for their bulk copies. The test hook makes the copies announce 16
+    bytes more than they bring, so the barrier of the first stage never completes: the kernel must give up after the
+    (shortened) bound, record the status word, leave D untouched and return -- no fault, no endless spin -- and the
+    entry points that read the word must report MMB200_ERR_TIMEOUT. The next call, with the hook cleared, works."""
+    L = _lib.load()
+    M, N, K = 256, 128, 512
+    rng = np.random.default_rng(9)
+    a = torch.from_numpy(datagen.codes(rng, M, K, "e4m3", "gauss40")).to(DEV)
+    b = torch.from_numpy(datagen.codes(rng, N, K, "e4m3", "gauss40")).to(DEV)
+    sc = torch.tensor([0.5, 2.0], dtype=torch.float32, device=DEV)
+    n = int(L.mmb200_workspace_bytes_split(M, N, K, 1))
+    ws = torch.zeros(n, dtype=torch.uint8, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+
+    def call(D):
+        return L.mmb200_scaled_mm_ws(a.data_ptr(), K, 0, b.data_ptr(), K, 0, D.data_ptr(), N, _lib.OUT_CODES["bfloat16"],
+                                     M, N, K, 32, 1, 1, 0, sc.data_ptr(), sc.data_ptr() + 4, None, 0, ws.data_ptr(), n,
+                                     stream)
+    L.mmb200_test_hooks(1000, 16)
+    try:
+        D = torch.full((M, N), 0x5555, dtype=torch.int16, device=DEV)
+        assert call(D) == _lib.OK                                  # the launch itself succeeds; it is asynchronous
+        assert L.mmb200_workspace_status(ws.data_ptr(), M, N, K, 1, stream) == _lib.ERR_TIMEOUT
+        assert bool((D == 0x5555).all())                           # nothing was written
+        off = int(L.mmb200_workspace_status_offset(M, N, K, 1))
+        assert int(ws[off:off + 4].view(torch.int32).item()) == 1
+        with pytest.raises(_lib.NativeError) as e:
+            _lib.check("mmb200_workspace_status", _lib.ERR_TIMEOUT)
+        assert e.value.status == _lib.ERR_TIMEOUT
+        # the host-buffer entry point synchronises anyway and must return the error instead of a stale result
+        ah, bh = a.cpu().numpy(), b.cpu().numpy()
+        dh = np.full((M, N), 0x5555, dtype=np.uint16)
+        rc = L.mmb200_scaled_mm_host(ah.ctypes.data, K, 0, bh.ctypes.data, K, 0, dh.ctypes.data, N,
+                                     _lib.OUT_CODES["bfloat16"], M, N, K, 32, 1, 1, 0, ctypes.c_float(0.5),
+                                     ctypes.c_float(2.0), None, 0, stream)
+        assert rc == _lib.ERR_TIMEOUT and bool((dh == 0x5555).all())
+        # the Python entry point checks the word when asked to
+        os.environ["MMAEMU_B200_CHECK_STATUS"] = "1"
+        with pytest.raises(_lib.NativeError):
+            mm.scaled_mm(a.view(torch.float8_e4m3fn), b.view(torch.float8_e4m3fn).t(), sc[0], sc[1],
+                         out_dtype=torch.bfloat16, use_fast_accum=True, profile="hopper", splitk=1)
+    finally:
+        os.environ.pop("MMAEMU_B200_CHECK_STATUS", None)
+        L.mmb200_test_hooks(0, 0)
+    D = torch.full((M, N), 0x5555, dtype=torch.int16, device=DEV)
+    assert call(D) == _lib.OK
+    assert L.mmb200_workspace_status(ws.data_ptr(), M, N, K, 1, stream) == _lib.OK
+    want = oracle.scaled_mm(a.cpu().numpy(), b.cpu().numpy(), 0.5, 2.0, out="bfloat16", preset=32, fast=True)
+    assert np.array_equal(D.cpu().numpy().view(np.uint16), want)
