@@ -2,53 +2,121 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (config 2 of the headline metric): profile 'hopper', M = N = K = 4096 per GPU, e4m3 x e4m3 operands from
-N(0, 1) * 4, tensor-wise fp32 scales 2^U(-4, 4), bf16 output, split-K 1, torch's default slow accumulation. With N > 1
-GPUs every rank computes its own 4096-row slab of a (4096 * N) x 4096 x 4096 call (weak scaling; the second operand is
-replicated) and the output slabs are assembled with one NCCL all-gather inside the timed step.
+One GPU (the headline, configuration 2 of the metric): profile 'hopper', M = N = K = 4096, e4m3 x e4m3 operands from
+N(0, 1) * 4, tensor-wise fp32 scales 2^U(-4, 4), bf16 output, split-K 1, torch's default slow accumulation. The same
+line carries, under "configs", the other configurations of the metric at their own sizes (the 256-cube under 'ada', the
+tall-skinny mixed-format shapes including table rows that split K, the FP8 projection stack under 'hopper-te', slabs of
+the sharded problem under 'hopper' and 'ada'), and under "context" the reference's own CUDA kernels (cuda:h4, cuda:h1)
+and torch._scaled_mm timed on the same GPU with the same method.
 
-One JSON line is printed by rank 0; see the keys below. `--impl reference` times the CPU restatement of the
-reference's model (the oracle) on the host's cores instead.
+N > 1 GPUs: STRONG scaling of one fixed problem with the recipe of the metric's sharded configuration -- e4m3 x e4m3,
+N(0, 1) * 16 operands with 1 % special codes (subnormals, +-max) and NaN codes in a seeded 1 % of the rows of both
+operands, fp16 output (overflow), use_fast_accum=True, profile 'hopper' -- at M = N = 16384, K = 8192 (a quarter of the
+metric's 32768 x 32768 x 8192 so that one GPU finishes a step in a quarter of a second). Rows are split across the
+ranks, every rank ends up with the whole result (mmaemu_b200.sharded_scaled_mm); before timing, all ranks compare a
+sha256 of the assembled result and rank 0 checks sampled rows of every rank's slab against the oracle.
+
+One JSON line is printed by rank 0. `--impl reference` times the reference's own CPU backend
+(mmaemu.scaled_mm(..., backend="reference") of the unmodified package under baseline/_ref) on all host cores on a
+bounded row sample of the same workload; without that package, the CPU restatement of the model (the oracle).
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import hashlib
 import json
 import os
 import subprocess
 import sys
 import threading
 import time
+import warnings
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "baseline"))
 
-M_PER_GPU, N_, K_ = 4096, 4096, 4096
-PROFILE, NFMA, FAST = "hopper", 32, False
 L2_FLUSH_BYTES = 512 << 20
 METRIC = "bit-exact emulated FP8 GEMM TFLOP/s (2MNK/t)"
+NFMA_OF = {"hopper": 32, "hopper-te": 32, "hopper-ws0": 32, "ada": 16, "ada-te": 16, "ada-ws0": 16}
 
-# Executed warp-instruction lanes per emulated multiply-accumulate of each kernel family, from the ncu captures
-# summarised under profiles/ (smsp__inst_executed.sum * 32 / (M*N*K) on the same workload).
-INST_PER_MAC = {"integer": None, "fast": 3.78, "staged": 2.78}
-# DRAM bytes per launch of the main kernel on the workload above, from a one-pass capture at full size
-# (dram__bytes_read.sum + dram__bytes_write.sum = 1,170,526,464 + 32,845,568); None where no capture exists.
-DRAM_TRAFFIC = {"integer": None, "fast": None, "staged": 1203372032}
+HEADLINE = dict(name="cfg2_hopper_4096cube", profile="hopper", M=4096, N=4096, K=4096, fa="e4m3", fb="e4m3",
+                out="bfloat16", fast=False, splitk=1)
+STRONG = dict(name="cfg5_recipe_16384x16384x8192", profile="hopper", M=16384, N=16384, K=8192, fa="e4m3", fb="e4m3",
+              out="float16", fast=True, splitk="auto", scale_a=1.0, scale_b=0.25)
+
+# Executed warp-instruction lanes per emulated multiply-accumulate, from ncu captures of the kernels as committed
+# (smsp__inst_executed.sum * 32 / (M*N*K), profiles/): keyed by (kernel, products per block, accumulation). A workload
+# whose kernel has no capture gets no issue-slot roofline (null), never another kernel's constant.
+INST_PER_MAC = {("staged_tc_kernel", 32, "slow"): None, ("staged_tc_kernel", 32, "fast"): None}
+# DRAM bytes per launch of the main kernel on the headline workload, one-pass ncu capture at full size (profiles/).
+DRAM_TRAFFIC = {("staged_tc_kernel", 32, "slow", 4096, 4096, 4096): None}
 
 
-def make_operands(rank: int):
-    """Seeded synthetic operands of the workload, as uint8 code tensors on the CPU, and the two scales."""
+# ---------------------------------------------------------------------------------------------------------------
+# data
+def _f8(name):
+    import torch
+    return torch.float8_e4m3fn if name == "e4m3" else torch.float8_e5m2
+
+
+def gaussian_codes(rows, K, sigma, seed, fmt="e4m3", device="cpu"):
+    """[rows, K] FP8 tensor from N(0, 1) * sigma, seeded."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    mx = 448.0 if fmt == "e4m3" else 57344.0
+    return (torch.randn(rows, K, generator=g, device=device) * sigma).clamp(-mx, mx).to(_f8(fmt))
+
+
+def headline_operands():
     import torch
     g = lambda s: torch.Generator().manual_seed(s)  # noqa: E731
-    a = (torch.randn(M_PER_GPU, K_, generator=g(2 + 1000 * rank)) * 4).clamp(-448, 448).to(torch.float8_e4m3fn)
-    bt = (torch.randn(N_, K_, generator=g(3)) * 4).clamp(-448, 448).to(torch.float8_e4m3fn)
+    c = HEADLINE
+    a = gaussian_codes(c["M"], c["K"], 4.0, 2)
+    bt = gaussian_codes(c["N"], c["K"], 4.0, 3)
     sa = (2.0 ** (torch.rand((), generator=g(4)) * 8 - 4)).to(torch.float32)
     sb = (2.0 ** (torch.rand((), generator=g(5)) * 8 - 4)).to(torch.float32)
     return a, bt, sa, sb
 
 
+def special_codes(rows, K, seed, device):
+    """E4M3 codes of the sharded configuration's recipe for `rows` rows: N(0, 1) * 16; 1 % of the elements replaced by a
+    subnormal code (0x01..0x07, either sign) or +-max (0x7E / 0xFE); NaN codes (0x7F / 0xFF) at three positions of a
+    seeded 1 % of the rows. Generated on `device` from `seed` (the same bytes on every GPU of one model)."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = (torch.randn(rows, K, generator=g, device=device) * 16).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    pick = torch.rand(rows, K, generator=g, device=device)
+    kind = torch.randint(0, 16, (rows, K), generator=g, device=device, dtype=torch.uint8)
+    sub = ((kind % 7) + 1) | ((kind & 8) << 4)                             # 0x01..0x07 with a random sign
+    top = torch.where((kind & 8) != 0, 0xFE, 0x7E).to(torch.uint8)
+    x = torch.where(pick < 0.005, sub, x)
+    x = torch.where((pick >= 0.005) & (pick < 0.01), top, x)
+    nan_rows = torch.nonzero(torch.rand(rows, generator=g, device=device) < 0.01).flatten()
+    if nan_rows.numel():
+        cols = torch.randint(0, K, (nan_rows.numel(), 3), generator=g, device=device)
+        x[nan_rows[:, None], cols] = torch.where(cols % 2 == 0, 0x7F, 0xFF).to(torch.uint8)
+    return x
+
+
+STRONG_CHUNKS = 8          # operand A of the strong-scaling problem is generated in 8 row chunks, one seed each
+
+
+def strong_a_rows(m0, m1, device):
+    """Rows [m0, m1) of the strong-scaling problem's first operand (whole chunks only)."""
+    import torch
+    per = STRONG["M"] // STRONG_CHUNKS
+    assert m0 % per == 0 and m1 % per == 0
+    return torch.cat([special_codes(per, STRONG["K"], 50 + c, device) for c in range(m0 // per, m1 // per)])
+
+
+def strong_bt(device):
+    return special_codes(STRONG["N"], STRONG["K"], 51_000, device)
+
+
+# ---------------------------------------------------------------------------------------------------------------
 class ClockSampler(threading.Thread):
     """Samples the SM clock and the throttle reasons of one GPU while the timed region runs: NVML every 5 ms when the
     pynvml module is present, else one nvidia-smi query per 100 ms. Read-only; nothing on the GPU is changed."""
@@ -125,237 +193,597 @@ class ClockSampler(threading.Thread):
         return out
 
 
-def cpu_baseline(a_u8, bt_u8, sa: float, sb: float, seconds: float = 12.0) -> dict:
-    """The oracle timed on the host's cores on a row subset of the workload sized for about `seconds` of CPU work."""
-    from oracle import oracle
-    threads = oracle.num_threads()
-    rows = 8
+# ---------------------------------------------------------------------------------------------------------------
+# the reference package (unmodified, under baseline/_ref) and the CPU arms
+def load_reference():
+    """The reference's `mmaemu` module from baseline/_ref, or None when it is not installed there."""
+    try:
+        import install_reference
+        if not install_reference.add_to_path():
+            return None
+        import mmaemu
+        return mmaemu
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:  # noqa: BLE001
+        return os.cpu_count() or 1
+
+
+def cpu_call(ref, a, bt, sa, sb, cfg, rows):
+    """One call of the CPU arm on the first `rows` rows of the workload: the reference's CPU backend when `ref` is the
+    reference module, else the oracle. Returns seconds."""
+    import torch
     t0 = time.perf_counter()
-    oracle.scaled_mm(a_u8[:rows], bt_u8, sa, sb, out="bfloat16", preset=NFMA, fast=FAST)
-    probe = time.perf_counter() - t0
-    rows = int(max(8, min(a_u8.shape[0], rows * seconds / max(probe, 1e-3))))
-    t0 = time.perf_counter()
-    oracle.scaled_mm(a_u8[:rows], bt_u8, sa, sb, out="bfloat16", preset=NFMA, fast=FAST)
-    dt = time.perf_counter() - t0
-    return {"value": 2.0 * rows * N_ * K_ / dt / 1e12, "unit": "TFLOP/s (emulated, 2MNK/t)", "cores": threads,
-            "kind": "port", "sample": f"first {rows} of {a_u8.shape[0]} rows x all {N_} columns x K={K_}, {dt:.1f} s",
-            "seconds": dt}
+    if ref is not None:
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            ref.scaled_mm(a[:rows], bt.t(), sa, sb, out_dtype=getattr(torch, cfg["out"]), use_fast_accum=cfg["fast"],
+                          profile=cfg["profile"], splitk=1, backend="reference")
+    else:
+        from oracle import oracle
+        oracle.scaled_mm(a[:rows].view(torch.uint8).numpy(), bt.view(torch.uint8).numpy(), float(sa), float(sb),
+                         out=cfg["out"], fmt_a=cfg["fa"], fmt_b=cfg["fb"], preset=NFMA_OF[cfg["profile"]],
+                         fast=cfg["fast"], threads=host_cores())
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(a, bt, sa, sb, cfg, seconds: float = 12.0) -> dict:
+    """The reference's CPU backend (kind "reference") -- or, without it, the oracle (kind "port") -- on all host cores,
+    on a row subset of the workload sized for about `seconds` of CPU work; plus the oracle port as a second figure."""
+    import torch
+    cores = host_cores()
+    torch.set_num_threads(cores)
+    ref = load_reference()
+    flops_per_row = 2.0 * cfg["N"] * cfg["K"]
+
+    def measure(impl, budget):
+        rows = 8
+        probe = cpu_call(impl, a, bt, sa, sb, cfg, rows)
+        rows = int(max(8, min(a.shape[0], rows * budget / max(probe, 1e-3))))
+        dt = cpu_call(impl, a, bt, sa, sb, cfg, rows)
+        return {"value": rows * flops_per_row / dt / 1e12, "unit": "TFLOP/s (emulated, 2MNK/t)", "cores": cores,
+                "sample": f"first {rows} of {a.shape[0]} rows x all {cfg['N']} columns x K={cfg['K']}, {dt:.1f} s",
+                "seconds": dt}
+    if ref is not None:
+        out = measure(ref, seconds)
+        out["kind"] = "reference"
+        out["what"] = "mmaemu.scaled_mm(..., backend='reference') of the unmodified reference on CPU tensors"
+        port = measure(None, 5.0)
+        port["kind"] = "port"
+        out["port"] = port
+    else:
+        out = measure(None, seconds)
+        out["kind"] = "port"
+        out["what"] = "the C restatement of the model (oracle/), OpenMP; the reference package is not under baseline/_ref"
+    return out
 
 
 def run_reference(args) -> int:
-    """The reference arm: the CPU restatement of the reference's model, all host threads, bounded sample per step."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference arm: the reference's own CPU implementation of the path, all host threads, a bounded row sample
+    of the headline workload per step. Under torchrun only rank 0 works."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return 0
-    a, bt, sa, sb = make_operands(0)
-    a_u8, bt_u8 = a.view(__import__("torch").uint8).numpy(), bt.view(__import__("torch").uint8).numpy()
-    from oracle import oracle
-    oracle.build()
-    rows = 16
-    times = []
+    import torch
+    cores = host_cores()
+    torch.set_num_threads(cores)
+    cfg = HEADLINE
+    a, bt, sa, sb = headline_operands()
+    ref = load_reference()
+    if ref is None:
+        from oracle import oracle
+        oracle.build()
+    rows, times = 16, []
     for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        oracle.scaled_mm(a_u8[:rows], bt_u8, float(sa), float(sb), out="bfloat16", preset=NFMA, fast=FAST)
-        dt = time.perf_counter() - t0
+        dt = cpu_call(ref, a, bt, sa, sb, cfg, rows)
         if i < args.warmup:
-            rows = int(max(16, min(M_PER_GPU, rows * 4.0 / max(dt, 1e-3))))     # about 4 s per step
+            rows = int(max(16, min(cfg["M"], rows * 4.0 / max(dt, 1e-3))))     # about 4 s per step
         else:
             times.append(dt)
     ms = 1e3 * sum(times) / len(times)
-    value = 2.0 * rows * N_ * K_ / (ms / 1e3) / 1e12
-    base = {"value": value, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
-            "sample": f"{rows} of {M_PER_GPU} rows x {N_} columns x K={K_} per step"}
+    value = 2.0 * rows * cfg["N"] * cfg["K"] / (ms / 1e3) / 1e12
+    kind = "reference" if ref is not None else "port"
+    base = {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"{rows} of {cfg['M']} rows x {cfg['N']} columns x K={cfg['K']} per step",
+            "what": "mmaemu.scaled_mm(..., backend='reference') on CPU tensors (unmodified reference package)"
+            if ref is not None else "C restatement of the model (the reference package is not under baseline/_ref)"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int32/fp32 (CPU integer model)", "data": "synthetic",
-        "config": {"workload": f"hopper e4m3xe4m3 {M_PER_GPU}x{N_}x{K_} bf16 slow-accum split-K 1, CPU row sample"},
+        "vs_baseline": None, "dtype": "float64 torch model on CPU" if ref is not None else "int32/fp32 (CPU integer model)",
+        "data": "synthetic", "config": {"workload": workload_text(cfg) + ", CPU row sample"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
     return 0
 
 
-def run_ours(args) -> int:
+# ---------------------------------------------------------------------------------------------------------------
+def workload_text(c) -> str:
+    return (f"profile {c['profile']}, {c['fa']}x{c['fb']}, M={c['M']} N={c['N']} K={c['K']}, {c['out']} out, "
+            f"use_fast_accum={c['fast']}, split-K {c['splitk']}")
+
+
+def kernel_of(cfg, S=1) -> str:
+    """Name of the main kernel the automatic choice runs for a configuration (with scratch memory)."""
+    return "staged_tc_kernel" if (cfg["fa"], cfg["fb"]) == ("e4m3", "e4m3") else "staged_kernel"
+
+
+class Timer:
+    """CUDA-event timing on torch's current stream with the L2 flushed between steps, outside the event pairs."""
+
+    def __init__(self, dev):
+        import torch
+        self.dev = dev
+        self.flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        self.stream = torch.cuda.current_stream(dev)
+
+    def total_ms(self, fn, steps) -> float:
+        import torch
+        pairs = []
+        for _ in range(steps):
+            self.flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            fn()
+            e1.record(self.stream)
+            pairs.append((e0, e1))
+        torch.cuda.synchronize(self.dev)
+        return sum(e0.elapsed_time(e1) for e0, e1 in pairs)
+
+    def median_ms(self, fn, steps, warm=2) -> float:
+        import torch
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(self.dev)
+        ts = sorted(self.total_ms(fn, 1) for _ in range(steps))
+        return ts[len(ts) // 2]
+
+
+def issue_peak(L, timer, clk_mhz):
+    """Peak of the roofline: lane-instructions per second the SMs issue. Measured live with the library's probe kernel
+    (independent round-toward-zero FMAs, 1024 threads per SM) and, beside it, the nominal 148 SMs x 128 lanes x clock."""
     import torch
-    import torch.distributed as dist
+    nominal = 148 * 128 * clk_mhz * 1e6 / 1e12
+    try:
+        iters, ctas = 4096, 148 * 8
+        stream = ctypes.c_void_p(timer.stream.cuda_stream)
+        sink = torch.zeros(ctas * 256, dtype=torch.float32, device=timer.dev)
+        run = lambda: L.mmb200_probe_issue_rate(0, ctas, iters, sink.data_ptr(), stream)  # noqa: E731
+        if run() != 0:
+            return nominal, {"nominal": nominal, "measured": None}
+        ms = timer.median_ms(run, 5)
+        ops = float(ctas) * 256 * iters * 32            # 32 independent FMAs per thread and iteration
+        return ops / (ms / 1e3) / 1e12, {"nominal": nominal, "measured_ffma_rz": ops / (ms / 1e3) / 1e12, "probe_ms": ms}
+    except Exception:  # noqa: BLE001
+        return nominal, {"nominal": nominal, "measured": None}
+
+
+def sampled_gate(mm, oracle, y, a_u8, bt_u8, sa, sb, cfg, S, scheme, label, rows=None, cols=None):
+    """Sampled rows and columns of a result against the oracle, bit for bit; raises SystemExit on a difference."""
+    import numpy as np
+    import torch
+    M, N = y.shape
+    rows = np.unique(np.linspace(0, M - 1, 12).astype(np.int64)) if rows is None else np.asarray(rows)
+    cols = np.unique(np.linspace(0, N - 1, 40).astype(np.int64)) if cols is None else np.asarray(cols)
+    view = {4: (torch.int32, np.uint32), 2: (torch.int16, np.uint16), 1: (torch.uint8, np.uint8)}[y.element_size()]
+    got = y[torch.as_tensor(rows, device=y.device)][:, torch.as_tensor(cols, device=y.device)].cpu().view(view[0]) \
+        .numpy().view(view[1])
+    want = oracle.scaled_mm(a_u8[rows], bt_u8[cols], float(sa), float(sb), out=cfg["out"], fmt_a=cfg["fa"],
+                            fmt_b=cfg["fb"], preset=NFMA_OF[cfg["profile"]], fast=cfg["fast"], S=S, scheme=scheme)
+    if not np.array_equal(got, want):
+        raise SystemExit(f"exactness gate failed ({label}): {int((got != want).sum())} of {want.size} sampled outputs "
+                         f"differ from the oracle; not timing")
+
+
+def time_config(mm, oracle, timer, dev, cfg, a, bt, sa, sb, steps=5):
+    """One configuration through mmaemu_b200.scaled_mm: gate on sampled outputs, then median device time."""
+    import torch
+    from mmaemu_b200.splitk import resolve_splitk
+    od = getattr(torch, cfg["out"])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        if cfg["splitk"] == "auto":
+            d = resolve_splitk(cfg["M"], cfg["N"], cfg["K"], a_dtype=cfg["fa"], b_dtype=cfg["fb"], out_dtype=cfg["out"],
+                               use_fast_accum=cfg["fast"], profile=cfg["profile"])
+            S, scheme = d.S, d.scheme
+        else:
+            S, scheme = 1, "none"
+        ad, bd = a.to(dev), bt.to(dev)
+        sad, sbd = torch.tensor(float(sa), device=dev), torch.tensor(float(sb), device=dev)
+        fn = lambda: mm.scaled_mm(ad, bd.t(), sad, sbd, out_dtype=od, use_fast_accum=cfg["fast"],  # noqa: E731
+                                  profile=cfg["profile"], splitk=cfg["splitk"])
+        y = fn()
+        torch.cuda.synchronize(dev)
+        sampled_gate(mm, oracle, y, a.view(torch.uint8).cpu().numpy(), bt.view(torch.uint8).cpu().numpy(), sa, sb, cfg,
+                     S, scheme, cfg["name"])
+        ms = timer.median_ms(fn, steps)
+    macs = float(cfg["M"]) * cfg["N"] * cfg["K"]
+    return {"workload": workload_text(cfg), "split": f"S={S} {scheme}", "ms": ms, "tflops": 2 * macs / (ms / 1e3) / 1e12,
+            "kernel": kernel_of(cfg, S), "exact_vs_oracle": True}
+
+
+def other_configs(mm, oracle, timer, dev, issue_peak_t):
+    """Configurations 1, 3, 4 and slabs of 5 at their own sizes (one GPU)."""
+    import torch
+    out = {}
+
+    def add(cfg, a, bt, sa, sb, steps=5):
+        r = time_config(mm, oracle, timer, dev, cfg, a, bt, sa, sb, steps)
+        ipm = INST_PER_MAC.get((r["kernel"], NFMA_OF[cfg["profile"]], "fast" if cfg["fast"] else "slow"))
+        r["roofline_frac"] = (float(cfg["M"]) * cfg["N"] * cfg["K"] * ipm / (r["ms"] / 1e3) / 1e12 / issue_peak_t
+                              if ipm else None)
+        out[cfg["name"]] = r
+    g = lambda s: torch.Generator().manual_seed(s)  # noqa: E731
+    # 1: ada, 256 cube
+    c = dict(name="cfg1_ada_256cube", profile="ada", M=256, N=256, K=256, fa="e4m3", fb="e4m3", out="bfloat16",
+             fast=False, splitk="auto")
+    add(c, (torch.randn(256, 256, generator=g(0)) * 2).to(torch.float8_e4m3fn),
+        torch.randn(256, 256, generator=g(1)).to(torch.float8_e4m3fn), 0.5, 1.25)
+    # 3: tall-skinny, e5m2 x e4m3, N(0, 1) * 8; two table shapes with S = 1 and two table rows that split K
+    for i, (prof, M, N, K, o, fast) in enumerate([("hopper", 128, 4096, 16384, "float32", False),
+                                                   ("hopper", 16, 4096, 8192, "bfloat16", False),
+                                                   ("hopper-te", 16, 8192, 28672, "bfloat16", False),
+                                                   ("hopper", 128, 128, 16384, "float32", True)]):
+        c = dict(name=f"cfg3_{prof}_{M}x{N}x{K}", profile=prof, M=M, N=N, K=K, fa="e5m2", fb="e4m3", out=o, fast=fast,
+                 splitk="auto")
+        add(c, gaussian_codes(M, K, 8.0, 6 + i, "e5m2"), gaussian_codes(N, K, 8.0, 20 + i, "e4m3"), 2.0 ** -5, 2.0 ** -4)
+    # 4: FP8 projection stack, hopper-te, amax-derived scales
+    for i, (N, K) in enumerate([(5760, 1920), (1920, 1920), (24576, 8192)]):
+        M = 8192
+        x = torch.randn(M, K, generator=g(40 + 3 * i))
+        w = torch.randn(N, K, generator=g(41 + 3 * i)) * 0.02
+        sx, sw = 448.0 / float(x.abs().max()), 448.0 / float(w.abs().max())
+        c = dict(name=f"cfg4_hopper-te_{M}x{N}x{K}", profile="hopper-te", M=M, N=N, K=K, fa="e4m3", fb="e4m3",
+                 out="bfloat16", fast=True, splitk="auto")
+        add(c, (x * sx).clamp(-448, 448).to(torch.float8_e4m3fn), (w * sw).clamp(-448, 448).to(torch.float8_e4m3fn),
+            1.0 / sx, 1.0 / sw, steps=3)
+    # 5: one 2048-row slab of the strong-scaling problem (what each of 8 GPUs computes), hopper and ada, and the whole
+    # strong-scaling problem on this one GPU (the N = 1 point of the strong-scaling curve)
+    bt = strong_bt(dev).view(torch.float8_e4m3fn)
+    a = strong_a_rows(0, STRONG["M"], dev).view(torch.float8_e4m3fn)
+    for prof in ("hopper", "ada"):
+        c = dict(STRONG, name=f"cfg5_slab_{prof}_2048x16384x8192", profile=prof, M=2048)
+        add(c, a[:2048], bt, STRONG["scale_a"], STRONG["scale_b"], steps=3)
+    add(dict(STRONG, name="cfg5_strong_n1"), a, bt, STRONG["scale_a"], STRONG["scale_b"], steps=3)
+    return out
+
+
+def reference_gpu_context(timer, dev, a_dev, bt_dev, sa_dev, sb_dev, y_ours, cfg):
+    """The reference's own CUDA kernels on this GPU, same operands, same timing method: the whole mmaemu.scaled_mm call
+    with the headline's arguments, and the chain kernel alone over the full K (one launch). Full outputs are compared
+    bit for bit with ours first. Context only."""
+    import torch
+    ref = load_reference()
+    if ref is None:
+        return {"unavailable": "the reference package is not installed under baseline/_ref"}
+    out = {}
+    od = getattr(torch, cfg["out"])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for name in ("h4", "h1"):
+            try:
+                call = lambda: ref.scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, out_dtype=od,  # noqa: E731
+                                             use_fast_accum=cfg["fast"], profile=cfg["profile"], splitk=1,
+                                             backend=f"cuda:{name}")
+                y = call()
+                torch.cuda.synchronize(dev)
+                same = bool(torch.equal(y.view(torch.int16), y_ours.view(torch.int16)))
+                ms = timer.median_ms(call, 5, warm=1)
+                from mmaemu.backends import ChainRequest
+                from mmaemu.backends.registry import select
+                req = ChainRequest(device=dev, fmt_a="e4m3", fmt_b="e4m3", preset="hopper")
+                chain = select(req, f"cuda:{name}").chain_fn(req)
+                au, bu = a_dev.view(torch.uint8), bt_dev.view(torch.uint8)
+                ms_chain = timer.median_ms(lambda: chain(au, bu), 5, warm=1)
+                flops = 2.0 * cfg["M"] * cfg["N"] * cfg["K"]
+                out[f"ref_{name}"] = {"whole_call_ms": ms, "value": flops / (ms / 1e3) / 1e12, "unit": "TFLOP/s",
+                                      "chain_kernel_alone_ms": ms_chain,
+                                      "chain_kernel_alone_tflops": flops / (ms_chain / 1e3) / 1e12,
+                                      "bit_identical_to_ours": same,
+                                      "what": f"mmaemu.scaled_mm(..., backend='cuda:{name}') of the unmodified reference, "
+                                              f"its stock loader; chain kernel = one launch over K={cfg['K']}"}
+            except Exception as e:  # noqa: BLE001
+                out[f"ref_{name}"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    try:
+        ms = timer.median_ms(lambda: torch._scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, out_dtype=od), 5)
+        out["native_scaled_mm"] = {"ms": ms, "value": 2.0 * cfg["M"] * cfg["N"] * cfg["K"] / (ms / 1e3) / 1e12,
+                                   "unit": "TFLOP/s", "what": "torch._scaled_mm on the B200's own tensor cores (other "
+                                                              "numerics; context only)"}
+    except Exception as e:  # noqa: BLE001
+        out["native_scaled_mm"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def run_one_gpu(args) -> int:
+    import numpy as np  # noqa: F401
+    import torch
     import mmaemu_b200 as mm
     from mmaemu_b200 import _lib
-    from mmaemu_b200.sharding import sharded_scaled_mm
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != max(1, args.gpus):
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch N > 1 with torch.distributed.run")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: mmaemu_b200 has no CPU fallback")
-    _lib.load()                                                # fails loudly if the CUDA library was never built
-    dev = torch.device("cuda", local)
+    from oracle import oracle
+    L = _lib.load()                                            # fails loudly if the CUDA library was never built
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    if world > 1:
-        import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    cfg = dict(HEADLINE)
+    if args.shape:
+        cfg.update(M=args.shape[0], N=args.shape[1], K=args.shape[2], name="custom")
+    if args.fast_accum:
+        cfg["fast"] = True
+    if args.profile:
+        cfg["profile"] = args.profile
+    default_workload = cfg == HEADLINE
     kernel = args.kernel
     backend = "cuda:b200" if kernel == "auto" else f"cuda:b200-{kernel}"
-    M_total = M_PER_GPU * world
-
-    a, bt, sa, sb = make_operands(rank)
+    if default_workload:
+        a, bt, sa, sb = headline_operands()
+    else:
+        a, bt = gaussian_codes(cfg["M"], cfg["K"], 4.0, 2), gaussian_codes(cfg["N"], cfg["K"], 4.0, 3)
+        sa, sb = torch.tensor(0.37), torch.tensor(1.9)
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    od = getattr(torch, cfg["out"])
+    es = torch.empty((), dtype=od).element_size()
     a_pin, bt_pin = a.view(torch.uint8).pin_memory(), bt.view(torch.uint8).pin_memory()
-    a_dev, bt_dev = a.to(dev), bt.to(dev)
-    sa_dev, sb_dev = sa.to(dev), sb.to(dev)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream(dev)
-    kw = dict(out_dtype=torch.bfloat16, use_fast_accum=FAST, profile=PROFILE, backend=backend, splitk=1)
-
-    def step_resident():
-        if world == 1:
-            return mm.scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, **kw)
-        return sharded_scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, input_is_local=True, full_rows=M_total, **kw)
-
-    out_pin = torch.empty((M_PER_GPU, N_), dtype=torch.bfloat16).pin_memory()
+    a_dev, bt_dev, sa_dev, sb_dev = a.to(dev), bt.to(dev), sa.to(dev), sb.to(dev)
+    timer = Timer(dev)
+    kw = dict(out_dtype=od, use_fast_accum=cfg["fast"], profile=cfg["profile"], backend=backend, splitk=1)
+    step = lambda: mm.scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, **kw)  # noqa: E731
+    out_pin = torch.empty((M, N), dtype=od).pin_memory()
 
     def step_e2e():
-        ad = a_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
-        bd = bt_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+        ad = a_pin.to(dev, non_blocking=True).view(a.dtype)
+        bd = bt_pin.to(dev, non_blocking=True).view(bt.dtype)
         y = mm.scaled_mm(ad, bd.t(), sa_dev, sb_dev, **kw)
         out_pin.copy_(y, non_blocking=True)
         return y
 
+    oracle.build()
+    y_gate = step()
+    torch.cuda.synchronize(dev)
+    if not args.skip_gate:
+        sampled_gate(mm, oracle, y_gate, a.view(torch.uint8).numpy(), bt.view(torch.uint8).numpy(), sa, sb, cfg, 1, "none",
+                     "headline")
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    total_ms = timer.total_ms(step, args.steps)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.summary()
+    for _ in range(2):
+        step_e2e()
+    torch.cuda.synchronize(dev)
+    e2e_ms = timer.total_ms(step_e2e, args.steps)
+    # the same through the C ABI's host-buffer entry point (pinned host operands in, pinned host result out; the call
+    # stages, computes and synchronises its stream itself, so it is timed on the host clock)
+    host_args = (a_pin.data_ptr(), K, _lib.FMT_CODES[cfg["fa"]], bt_pin.data_ptr(), K, _lib.FMT_CODES[cfg["fb"]],
+                 out_pin.data_ptr(), N, _lib.OUT_CODES[cfg["out"]], M, N, K, NFMA_OF[cfg["profile"]], int(cfg["fast"]), 1,
+                 0, ctypes.c_float(float(sa)), ctypes.c_float(float(sb)), None, 0,
+                 ctypes.c_void_p(timer.stream.cuda_stream))
+    for _ in range(2):
+        _lib.check("mmb200_scaled_mm_host", L.mmb200_scaled_mm_host(*host_args))
+    torch.cuda.synchronize(dev)
+    t_host = time.perf_counter()
+    for _ in range(args.steps):
+        _lib.check("mmb200_scaled_mm_host", L.mmb200_scaled_mm_host(*host_args))
+    host_ms = (time.perf_counter() - t_host) * 1e3
+
+    ms = total_ms / args.steps
+    macs = float(M) * N * K
+    value = 2.0 * macs / (ms / 1e3) / 1e12
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:  # noqa: BLE001
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    auto = L.mmb200_kernel_for(a_dev.data_ptr(), K, bt_dev.data_ptr(), K, K, NFMA_OF[cfg["profile"]], 1)
+    if kernel == "integer" or (kernel == "auto" and auto != _lib.KERNEL_CODES["fast"]):
+        used = "integer_kernel"
+    elif os.environ.get("MMAEMU_B200_WORKSPACE", "1") == "0":
+        used = "fast_kernel"
+    else:
+        used = kernel_of(cfg)
+    clk_mhz = clocks.get("sm_mhz") or float(peaks.get("sm_max_mhz", 1965.0))
+    peak_t, peak_info = issue_peak(L, timer, clk_mhz)
+    key = (used, NFMA_OF[cfg["profile"]], "fast" if cfg["fast"] else "slow")
+    ipm = INST_PER_MAC.get(key)
+    achieved = macs * ipm / (ms / 1e3) / 1e12 if ipm else None
+    algo_bytes = M * K + N * K + M * N * es + 12
+    algo_ops = 4 + 12 / NFMA_OF[cfg["profile"]]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "int32" if used == "integer_kernel" else "fp32 round-toward-zero FMA + int32 (exact emulation of fp8 x "
+                                                         "fp8 blocks)",
+        "data": "synthetic",
+        "config": {"workload": workload_text(cfg) + f", kernel {used}", "profile": cfg["profile"],
+                   "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)", "multi_gpu": "single GPU"},
+        "roofline": {"bound": "alu-issue", "kernel": used, "achieved": achieved, "peak": peak_t,
+                     "unit": "T lane-instructions/s", "frac": achieved / peak_t if achieved else None,
+                     "traffic": DRAM_TRAFFIC.get(key + (M, N, K)),
+                     "peak_basis": "lane-instructions per second of independent fma.rz.f32 measured in this run with the "
+                                   "library's probe kernel (FP32 pipe: 128 lanes per clock and SM; the INT32 ALU pipe "
+                                   "issues 64)", "peak_detail": peak_info, "inst_per_mac": ipm,
+                     "note": None if ipm else "no ncu capture of this kernel and accumulation mode: no issue-slot figure",
+                     "algorithmic_ops_per_mac": algo_ops,
+                     "algorithmic_achieved": macs * algo_ops / (ms / 1e3) / 1e12,
+                     "hbm": {"achieved_gbs": algo_bytes / (ms / 1e3) / 1e9, "peak_gbs": hbm_peak,
+                             "frac": algo_bytes / (ms / 1e3) / 1e9 / hbm_peak,
+                             "of": "measured" if "hbm_gbs" in peaks else "fallback"}},
+        "e2e": {"value": 2.0 * macs / (e2e_ms / args.steps / 1e3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": (M + N) * K, "d2h_bytes_per_step": M * N * es, "ms_per_step": e2e_ms / args.steps,
+                "call": "mmaemu_b200.scaled_mm on operands copied from pinned host memory each step, result copied "
+                        "back to pinned host memory",
+                "c_abi_host_call": {"value": 2.0 * macs / (host_ms / args.steps / 1e3) / 1e12, "unit": "TFLOP/s",
+                                    "ms_per_step": host_ms / args.steps,
+                                    "call": "mmb200_scaled_mm_host: pinned host operands in, pinned host result out, "
+                                            "device staging inside the call, host clock"}},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if default_workload and not args.headline_only:
+        sampler2 = ClockSampler(dev.index)
+        sampler2.start()
+        line["context"] = reference_gpu_context(timer, dev, a_dev, bt_dev, sa_dev, sb_dev, y_gate, cfg)
+        line["context"]["clocks"] = sampler2.summary()
+        sampler3 = ClockSampler(dev.index)
+        sampler3.start()
+        line["configs"] = other_configs(mm, oracle, timer, dev, peak_t)
+        line["configs"]["clocks"] = sampler3.summary()
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(a, bt, sa, sb, cfg)
+    print(json.dumps(line))
+    return 0
+
+
+def run_multi_gpu(args) -> int:
+    import datetime
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import mmaemu_b200 as mm
+    from mmaemu_b200 import _lib
+    from mmaemu_b200.sharding import shard_rows, sharded_scaled_mm
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch N > 1 with torch.distributed.run")
+    _lib.load()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+    cfg = STRONG
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    od = getattr(torch, cfg["out"])
+    m0, m1 = shard_rows(M, world, rank)
+    a_dev = strong_a_rows(m0, m1, dev).view(torch.float8_e4m3fn)
+    bt_dev = strong_bt(dev).view(torch.float8_e4m3fn)
+    sa_dev, sb_dev = torch.tensor(cfg["scale_a"], device=dev), torch.tensor(cfg["scale_b"], device=dev)
+    timer = Timer(dev)
+    kw = dict(out_dtype=od, use_fast_accum=cfg["fast"], profile=cfg["profile"], splitk=cfg["splitk"],
+              input_is_local=True, full_rows=M, assemble=args.assemble)
+
     def sync_all():
         torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize(dev)
-
-    def timed(fn, steps):
-        """Sum of per-step device times (CUDA events on the launch stream); L2 is flushed between steps, outside the
-        event pairs."""
-        pairs = []
-        for _ in range(steps):
-            flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            fn()
-            e1.record(stream)
-            pairs.append((e0, e1))
+        dist.barrier()
         torch.cuda.synchronize(dev)
-        return sum(e0.elapsed_time(e1) for e0, e1 in pairs)
 
-    # exactness gate before timing: sampled rows and columns of the full output against the oracle
+    def step():
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            return sharded_scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, **kw)
+
+    def step_compute_only():
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            return sharded_scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, gather=False, **kw)
+
+    a_pin, bt_pin = a_dev.view(torch.uint8).cpu().pin_memory(), bt_dev.view(torch.uint8).cpu().pin_memory()
+    out_pin = torch.empty((m1 - m0, N), dtype=od).pin_memory()
+
+    def step_e2e():
+        ad = a_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+        bd = bt_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            y = sharded_scaled_mm(ad, bd.t(), sa_dev, sb_dev, **kw)
+        out_pin.copy_(y[m0:m1], non_blocking=True)
+        return y
+
+    # ---- verification before timing: every rank holds the same assembled result; rank 0 checks rows of every slab
+    y = step()
+    sync_all()
+    digest = hashlib.sha256(y.view(torch.int16).cpu().numpy().tobytes()).hexdigest()
+    digests = [None] * world
+    dist.all_gather_object(digests, digest)
+    if len(set(digests)) != 1:
+        raise SystemExit(f"assembled results differ between ranks: {digests}")
+    gate = {"sha256_equal_on_all_ranks": True, "sha256": digest[:16]}
     if rank == 0 and not args.skip_gate:
-        import numpy as np
         from oracle import oracle
         oracle.build()
-        y = mm.scaled_mm(a_dev, bt_dev.t(), sa_dev, sb_dev, **kw)      # this rank's slab; no collective in the gate
-        torch.cuda.synchronize(dev)
-        rows = torch.arange(0, M_PER_GPU, max(1, M_PER_GPU // 12 - 1))[:12]
-        cols = torch.arange(0, N_, max(1, N_ // 40 - 1))[:40]
-        got = y[rows][:, cols].cpu().view(torch.int16).numpy().view(np.uint16)
-        want = oracle.scaled_mm(a.view(torch.uint8).numpy()[rows.numpy()], bt.view(torch.uint8).numpy()[cols.numpy()],
-                                float(sa), float(sb), out="bfloat16", preset=NFMA, fast=FAST)
-        if not np.array_equal(got, want):
-            raise SystemExit("exactness gate failed: the kernel's output differs from the oracle; not timing")
-
+        bt_u8 = bt_pin.numpy()
+        checked = 0
+        for r in range(world):
+            r0, r1 = shard_rows(M, world, r)
+            a_r = strong_a_rows(r0, r1, dev)
+            nan_rows = torch.nonzero(((a_r & 0x7F) == 0x7F).any(dim=1)).flatten()[:2].cpu().numpy()
+            rows = np.unique(np.concatenate([np.array([0, (r1 - r0) // 2 + 1, r1 - r0 - 1]), nan_rows]))
+            nan_cols = np.nonzero(((bt_u8 & 0x7F) == 0x7F).any(axis=1))[0][:3]
+            cols = np.unique(np.concatenate([np.linspace(0, N - 1, 45).astype(np.int64), nan_cols]))
+            sampled_gate(mm, oracle, y[r0:r1], a_r.cpu().numpy(), bt_u8, cfg["scale_a"], cfg["scale_b"], cfg, 1, "none",
+                         f"slab of rank {r}", rows=rows, cols=cols)
+            checked += rows.size * cols.size
+        inf = int(((y.view(torch.int16) & 0x7FFF) == 0x7C00).sum())
+        nan = int(((y.view(torch.int16) & 0x7FFF) > 0x7C00).sum())
+        gate.update(oracle_sampled_outputs=checked, fp16_inf_outputs=inf, nan_outputs=nan)
+        sys.stderr.write(f"gate: all {world} ranks hold sha256 {digest[:16]}...; {checked} sampled outputs of every slab "
+                         f"equal the oracle; {inf} outputs overflowed fp16, {nan} are NaN\n")
+    del y
     for _ in range(max(3, args.warmup)):
-        step_resident()
+        step()
     sync_all()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()
     sync_all()
-    total_ms = timed(step_resident, args.steps)
+    total_ms = timer.total_ms(step, args.steps)
     sync_all()
     launches = _lib.launch_count() - launches0
     clocks = sampler.summary() if rank == 0 else None
-
+    compute_ms = timer.total_ms(step_compute_only, args.steps)
+    sync_all()
     for _ in range(2):
         step_e2e()
     sync_all()
-    e2e_ms = timed(step_e2e, args.steps)
+    e2e_ms = timer.total_ms(step_e2e, args.steps)
     sync_all()
-
-    # the same through the C ABI's host-buffer entry point (pinned host operands in, pinned host result out; the call
-    # stages, computes and synchronises its stream itself, so it is timed on the host clock)
-    L = _lib.load()
-    host_args = (a_pin.data_ptr(), K_, 0, bt_pin.data_ptr(), K_, 0, out_pin.data_ptr(), N_, 1, M_PER_GPU, N_, K_, NFMA,
-                 int(FAST), 1, 0, ctypes.c_float(float(sa)), ctypes.c_float(float(sb)), None, 0,
-                 ctypes.c_void_p(stream.cuda_stream))
-    for _ in range(2):
-        _lib.check("mmb200_scaled_mm_host", L.mmb200_scaled_mm_host(*host_args))
-    sync_all()
-    t_host = time.perf_counter()
-    for _ in range(args.steps):
-        _lib.check("mmb200_scaled_mm_host", L.mmb200_scaled_mm_host(*host_args))
-    host_ms = (time.perf_counter() - t_host) * 1e3
-    sync_all()
-
-    t = torch.tensor([total_ms, e2e_ms, host_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, host_ms = (float(x) for x in t.cpu())
-    ms = total_ms / args.steps
-    macs = float(M_total) * N_ * K_
-    value = 2.0 * macs / (ms / 1e3) / 1e12
-    e2e_value = 2.0 * macs / (e2e_ms / args.steps / 1e3) / 1e12
-
+    t = torch.tensor([total_ms, e2e_ms, compute_ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, compute_ms = (float(x) for x in t.cpu())
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
-        except Exception:  # noqa: BLE001
-            pass
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        auto = _lib.load().mmb200_kernel_for(a_dev.data_ptr(), K_, bt_dev.data_ptr(), K_, K_, NFMA, 1)
-        used = kernel if kernel != "auto" else ("fast" if auto == _lib.KERNEL_CODES["fast"] else "integer")
-        if used == "fast" and os.environ.get("MMAEMU_B200_WORKSPACE", "1") != "0":
-            used = "staged"                                        # operands decoded once into scratch memory
-        clk_mhz = (clocks or {}).get("sm_mhz") or float(peaks.get("sm_max_mhz", 1965.0))
-        issue_peak = 148 * 128 * clk_mhz * 1e6 / 1e12                 # T lane-instructions / s at the sampled SM clock
-        per_gpu_macs = float(M_PER_GPU) * N_ * K_
-        kernel_s = ms / 1e3
-        ipm = INST_PER_MAC[used]
-        achieved_issue = per_gpu_macs * ipm / kernel_s / 1e12 if ipm else None
-        algo_bytes = M_PER_GPU * K_ + N_ * K_ + M_PER_GPU * N_ * 2 + 12
+        from mmaemu_b200 import sharding
+        ms = total_ms / args.steps
+        macs = float(M) * N * K
+        es = torch.empty((), dtype=od).element_size()
+        mode = args.assemble
+        if mode == "auto":
+            mode = "nccl" if any(sharding._symm_failed.values()) or not sharding._symm_cache else "peer"
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp32 round-toward-zero FMA + int32 (exact emulation of fp8 x fp8 blocks)"
-            if used != "integer" else "int32", "data": "synthetic",
-            "config": {"workload": f"profile {PROFILE}, e4m3xe4m3, M={M_total} N={N_} K={K_} ({M_PER_GPU} rows per GPU), "
-                                   f"bf16 out, split-K 1, use_fast_accum={FAST}, kernel {used}",
-                       "profile": PROFILE,
-                       "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)",
-                       "multi_gpu": "row slabs + one NCCL all-gather per step" if world > 1 else "single GPU"},
-            "roofline": {"bound": "alu-issue", "achieved": achieved_issue, "peak": issue_peak,
-                         "unit": "T lane-instructions/s",
-                         "frac": achieved_issue / issue_peak if achieved_issue else None,
-                         "traffic": DRAM_TRAFFIC[used],
-                         "peak_basis": f"148 SMs x 128 lanes x {clk_mhz:.0f} MHz sampled under load (measured issue "
-                                       f"rate of FFMA on this pool: 128 lanes/clk/SM; INT32 ALU pipe 64)",
-                         "inst_per_mac": INST_PER_MAC[used],
-                         "algorithmic_ops_per_mac": 4 + 12 / NFMA,
-                         "algorithmic_achieved": per_gpu_macs * (4 + 12 / NFMA) / kernel_s / 1e12,
-                         "hbm": {"achieved_gbs": algo_bytes / kernel_s / 1e9, "peak_gbs": hbm_peak,
-                                 "frac": algo_bytes / kernel_s / 1e9 / hbm_peak, "of": "measured"
-                                 if "hbm_gbs" in peaks else "fallback"}},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": (M_PER_GPU + N_) * K_,
-                    "d2h_bytes_per_step": M_PER_GPU * N_ * 2, "ms_per_step": e2e_ms / args.steps,
-                    "call": "mmaemu_b200.scaled_mm on operands copied from pinned host memory each step, result "
-                            "copied back to pinned host memory",
-                    "c_abi_host_call": {"value": 2.0 * macs / (host_ms / args.steps / 1e3) / 1e12, "unit": "TFLOP/s",
-                                        "ms_per_step": host_ms / args.steps,
-                                        "call": "mmb200_scaled_mm_host: pinned host operands in, pinned host result "
-                                                "out, device staging inside the call, host clock"}},
+            "metric": METRIC, "value": 2.0 * macs / (ms / 1e3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp32 round-toward-zero FMA + int32 (exact emulation of fp8 x fp8 blocks)", "data": "synthetic",
+            "config": {"workload": workload_text(cfg) + f"; the sharded configuration's recipe (1 % special codes, NaN rows, "
+                                   f"fp16 overflow) at a quarter of its 32768 x 32768 x 8192; rows split over {world} "
+                                   f"GPUs ({m1 - m0} each), every GPU ends up with the whole result",
+                       "profile": cfg["profile"], "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)",
+                       "multi_gpu": {"peer": "the kernel's epilogue stores each output into every GPU's copy of the "
+                                             "result through peer pointers (symmetric memory, NVLink); a device-side "
+                                             "barrier before and after; the result is returned as a copy",
+                                     "nccl": "row slabs + one NCCL all-gather per step"}[mode],
+                       "n1_point": "the same problem on one GPU is `configs.cfg5_strong_n1` of the --gpus 1 line"},
+            "compute_only_ms_per_step": compute_ms / args.steps,
+            "assembly_exposed_ms_per_step": ms - compute_ms / args.steps,
+            "gate": gate,
+            "e2e": {"value": 2.0 * macs / (e2e_ms / args.steps / 1e3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": ((m1 - m0) + N) * K, "d2h_bytes_per_step": (m1 - m0) * N * es,
+                    "ms_per_step": e2e_ms / args.steps,
+                    "call": "mmaemu_b200.sharded_scaled_mm on this rank's rows of A and all of B copied from pinned host "
+                            "memory each step (bytes per rank), this rank's rows of the assembled result copied back"},
             "gpu_launches": int(launches), "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(a.view(torch.uint8).numpy(), bt.view(torch.uint8).numpy(), float(sa),
-                                                float(sb))
         print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    dist.barrier()
+    dist.destroy_process_group()
     return 0
 
 
@@ -367,22 +795,25 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--kernel", choices=("auto", "integer", "fast"), default="auto")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
-                    help="per-GPU problem size instead of the headline 4096 4096 4096 (profiling runs)")
+                    help="problem size instead of the headline 4096 4096 4096 (profiling runs, one GPU)")
     ap.add_argument("--fast-accum", action="store_true", help="use_fast_accum=True instead of torch's default")
     ap.add_argument("--profile", default=None, help="emulated platform profile (default hopper)")
     ap.add_argument("--skip-gate", action="store_true", help="skip the exactness gate before timing")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true", help="one GPU: skip the context and the other configurations")
+    ap.add_argument("--assemble", choices=("auto", "peer", "nccl"), default="auto",
+                    help="N > 1: how the result is assembled on every GPU")
     args = ap.parse_args()
-    global M_PER_GPU, N_, K_, FAST, PROFILE, NFMA
-    if args.shape:
-        M_PER_GPU, N_, K_ = args.shape
-    if args.fast_accum:
-        FAST = True
-    if args.profile:
-        PROFILE, NFMA = args.profile, (16 if args.profile.startswith("ada") else 32)
     if args.impl == "reference":
         return run_reference(args)
-    return run_ours(args)
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: mmaemu_b200 has no CPU fallback")
+    if max(1, args.gpus) == 1:
+        if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+            raise SystemExit("--gpus 1 but WORLD_SIZE > 1")
+        return run_one_gpu(args)
+    return run_multi_gpu(args)
 
 
 if __name__ == "__main__":

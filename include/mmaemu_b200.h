@@ -66,6 +66,7 @@ extern "C" {
 #define MMB200_KERNEL_FAST 2     /* fp32 round-toward-zero FMA chain with integer corrections */
 
 #define MMB200_MAX_SPLITS 64
+#define MMB200_MAX_PEERS 15      /* other GPUs that can receive a copy of the output (mmb200_scaled_mm_peers) */
 
 int mmb200_abi_version(void);
 const char *mmb200_status_string(int status);
@@ -128,6 +129,22 @@ int mmb200_accumulate_ws(const void *A_dev, int64_t lda, int fmt_a, const void *
                          float *C_dev, int64_t ldc, int M, int N, int K, int nfma, int fast, int S, int scheme,
                          int kernel, void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* Multi-GPU assembly fused into the kernel. Large calls are split by output rows (or by any output rectangle: pass the
+ * operand and output pointers of the rectangle's first element with the full leading dimensions) across the GPUs of one
+ * machine, K is never split across GPUs, and every GPU needs the whole result. Instead of an all-gather after the
+ * kernel, mmb200_scaled_mm_peers stores every output element of this GPU's rectangle into D_dev and, at the same
+ * index, into each of the n_peers buffers peer_D[i]: device pointers, valid in this process, to the same rectangle of
+ * the other GPUs' result buffers (peer-mapped memory, e.g. symmetric memory or CUDA IPC; plain stores over NVLink, no
+ * multicast, no loads from peer memory). The caller orders the kernels on all GPUs against the readers with its own
+ * barrier after the call (and before it, if the buffers are being reused). n_peers = 0 is mmb200_scaled_mm_ws.
+ * `peer_D` is a HOST array of n_peers device pointers (read during the call). The reference has no multi-GPU path
+ * (docs/limitations.md:100 of astding/mmaemu). */
+int mmb200_scaled_mm_peers(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
+                           void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
+                           int scheme, const float *scale_a_dev, const float *scale_b_dev,
+                           const float *scale_result_dev, int kernel, void *workspace_dev, size_t workspace_bytes,
+                           void *const *peer_D, int n_peers, void *stream);
+
 /* Bounded waits and their status word. The scratch-memory kernels wait for their bulk copies on mbarriers with a bound
  * (about four seconds); a wait that runs out makes the kernel record 1 in a status word inside the scratch memory, skip
  * the output (D keeps its previous contents) and return, instead of spinning forever. Launches are asynchronous, so the
@@ -183,6 +200,13 @@ int mmb200_scaled_mm_static(const void *A_dev, int64_t lda, int fmt_a, const voi
  * the *_ws entry points serve split plans on the fast kernels too). Pure host logic: no CUDA call, nothing is dereferenced. It has no
  * counterpart in the reference, whose kernels each serve one format pair and one preset (mmaemu/backends/registry.py). */
 int mmb200_kernel_for(const void *A_dev, int64_t lda, const void *B_dev, int64_t ldb, int K, int nfma, int S);
+
+/* Issue-rate probe for roofline denominators: launches `ctas` blocks of 256 threads in which every thread executes
+ * iters x 32 independent instructions of one kind (kind 0: fma.rz.f32; kind 1: three-input integer add and three-input
+ * logic operation alternating) and stores one float per thread to sink_dev (ctas * 256 floats). The caller times the
+ * launch; lane-instructions = ctas * 256 * iters * 32. Not counted by mmb200_launch_count. The reference measures its
+ * kernels' rates with a host script instead (tools/bench_kernels.py:271-350 of astding/mmaemu). */
+int mmb200_probe_issue_rate(int kind, int ctas, int iters, float *sink_dev, void *stream);
 
 /* Number of kernel launches the library has issued in this process (all threads), for launch accounting. */
 int64_t mmb200_launch_count(void);

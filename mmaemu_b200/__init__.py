@@ -27,6 +27,7 @@ _LAZY = {
     "get_preset": ("mmaemu_b200.numerics", "get_preset"), "Preset": ("mmaemu_b200.numerics", "Preset"),
     "B200Backend": ("mmaemu_b200.backend", "B200Backend"), "BACKEND": ("mmaemu_b200.backend", "BACKEND"),
     "sharded_scaled_mm": ("mmaemu_b200.sharding", "sharded_scaled_mm"),
+    "scaled_mm_into": ("mmaemu_b200.api", "scaled_mm_into"),
 }
 
 __all__ = ["__version__", *sorted(_LAZY), "MmaemuError", "ReferenceRejectsError", "UnsupportedFeatureError",

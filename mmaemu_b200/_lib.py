@@ -24,7 +24,7 @@ EXPORTS = ("mmb200_abi_version", "mmb200_status_string", "mmb200_last_cuda_error
            "mmb200_chain", "mmb200_accumulate", "mmb200_scaled_mm", "mmb200_scaled_mm_host", "mmb200_kernel_for",
            "mmb200_launch_count", "mmb200_workspace_bytes", "mmb200_workspace_bytes_split", "mmb200_scaled_mm_ws", "mmb200_accumulate_ws",
            "mmb200_scaled_mm_static", "mmb200_quantize_scaled_mm_ws", "mmb200_workspace_status_offset",
-           "mmb200_workspace_status", "mmb200_scaled_mm_static_status", "mmb200_test_hooks")
+           "mmb200_workspace_status", "mmb200_scaled_mm_static_status", "mmb200_test_hooks", "mmb200_scaled_mm_peers", "mmb200_probe_issue_rate")
 
 _lock = threading.Lock()
 _lib = None
@@ -86,6 +86,11 @@ def load():
         L.mmb200_accumulate_ws.restype = ci
         L.mmb200_scaled_mm_static.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, vp, vp, vp, vp]
         L.mmb200_scaled_mm_static.restype = ci
+        L.mmb200_scaled_mm_peers.argtypes = [vp, i64, ci, vp, i64, ci, vp, i64, ci, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp,
+                                             ci, vp, ctypes.c_size_t, vp, ci, vp]
+        L.mmb200_scaled_mm_peers.restype = ci
+        L.mmb200_probe_issue_rate.argtypes = [ci, ci, ci, vp, vp]
+        L.mmb200_probe_issue_rate.restype = ci
         L.mmb200_workspace_status_offset.argtypes = [ci, ci, ci, ci]
         L.mmb200_workspace_status_offset.restype = ctypes.c_size_t
         L.mmb200_workspace_status.argtypes = [vp, ci, ci, ci, ci, vp]

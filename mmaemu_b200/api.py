@@ -35,7 +35,7 @@ from .numerics import check_plan, get_preset
 from .platforms import get_profile, profile_maturity_warning
 from .splitk import resolve_splitk
 
-__all__ = ["scaled_mm", "accumulate", "explain", "CallPlan", "BACKEND_NAMES"]
+__all__ = ["scaled_mm", "scaled_mm_into", "accumulate", "explain", "CallPlan", "BACKEND_NAMES"]
 
 BACKEND_NAMES = ("auto", "cuda", "cuda:b200", "cuda:b200-integer", "cuda:b200-fast", "cuda:b200-direct")
 # kernel family behind each backend name; "direct" = automatic choice without scratch memory (operands are decoded
@@ -307,25 +307,32 @@ def _kernel_code(kernel: str) -> int:
     return _lib.KERNEL_CODES["auto" if kernel == "direct" else kernel]
 
 
-def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -> torch.Tensor:
+def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool, y=None, peers=()) -> torch.Tensor:
+    """The one call into the library. y: where the result goes (default: a new [M, N] tensor): row-major with unit
+    stride along N. peers: device pointers, valid in this process, that receive the same elements at the same indices
+    (the same [M, N] rectangle of other GPUs' result buffers)."""
     dev = c.mat1.device
     a = c.mat1.detach()
     bt = mat2.detach().t()                               # [N, K] with unit stride along K
     lda = a.stride(0) if c.M > 1 else c.K
     ldb = bt.stride(0) if c.N > 1 else c.K
-    y = torch.empty((c.M, c.N), dtype=c.od, device=dev)
+    if y is None:
+        y = torch.empty((c.M, c.N), dtype=c.od, device=dev)
+    ldd = y.stride(0) if c.M > 1 else c.N
     keep_a, pa = _scalar_ptr(scale_a, dev)
     keep_b, pb = _scalar_ptr(scale_b, dev)
     keep_r, pr = (None, None) if scale_result is None else _scalar_ptr(scale_result, dev)
     L = _lib.load()
+    peer_array = (ctypes.c_void_p * max(len(peers), 1))(*[ctypes.c_void_p(int(p)) for p in peers])
     with torch.cuda.device(dev):
         ws, ws_ptr, ws_bytes = _workspace(L, c.kernel, a.data_ptr(), lda, bt.data_ptr(), ldb, c.M, c.N, c.K,
                                           c.preset.nfma, c.decision.S, dev)
-        rc = L.mmb200_scaled_mm_ws(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb, _lib.FMT_CODES[c.fb],
-                                   y.data_ptr(), c.N, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K,
-                                   c.preset.nfma, int(fast), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb, pr,
-                                   _kernel_code(c.kernel), ws_ptr, ws_bytes, _stream_ptr(dev))
-    _lib.check("mmb200_scaled_mm_ws", rc)
+        rc = L.mmb200_scaled_mm_peers(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb,
+                                      _lib.FMT_CODES[c.fb], y.data_ptr(), ldd, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]],
+                                      c.M, c.N, c.K, c.preset.nfma, int(fast), c.decision.S,
+                                      _lib.SCHEME_CODES[c.scheme], pa, pb, pr, _kernel_code(c.kernel), ws_ptr, ws_bytes,
+                                      peer_array, len(peers), _stream_ptr(dev))
+    _lib.check("mmb200_scaled_mm_peers", rc)
     if ws is not None and os.environ.get("MMAEMU_B200_CHECK_STATUS", "0") == "1":
         # opt-in: wait for the call and read the status word of its bounded waits (a host synchronisation per call)
         with torch.cuda.device(dev):
@@ -333,6 +340,31 @@ def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool) -
                                                                             _stream_ptr(dev)))
     del keep_a, keep_b, keep_r, ws
     return y
+
+
+def scaled_mm_into(y, peers, input, mat2, scale_a, scale_b, scale_result=None, use_fast_accum=False, *, profile=None,
+                   splitk="auto", backend="auto"):
+    """scaled_mm whose result is written into `y` -- an [M, N] row-major tensor or view (unit stride along N; any row
+    stride, so a rectangle of a larger result works) -- and, element for element, into the memory at every device
+    pointer of `peers` (the same rectangle of other GPUs' result buffers, mapped into this process). The building
+    block of sharded_scaled_mm's fused assembly. Every check and raise is scaled_mm's, with out_dtype = y.dtype."""
+    if not isinstance(y, torch.Tensor) or y.dim() != 2 or (y.shape[1] > 1 and y.stride(1) != 1):
+        raise TypeError("scaled_mm_into(): y must be a 2-D tensor with unit stride along its last dimension")
+    c = _prepare(input, mat2, scale_a, scale_b, None, scale_result, y.dtype, use_fast_accum, None, profile, splitk,
+                 backend, dry=False)
+    if tuple(y.shape) != (c.M, c.N):
+        raise ValueError(f"scaled_mm_into(): y has shape {tuple(y.shape)}, the result is {(c.M, c.N)}")
+    if y.device != input.device:
+        raise ValueError(f"scaled_mm_into(): y is on {y.device}, the operands on {input.device}")
+    if c.M == 0 or c.N == 0:
+        return y
+    if c.early:                                          # K == 0: +0 everywhere; peers are written by their own ranks' calls
+        y.zero_()
+        if peers:
+            raise ValueError("scaled_mm_into(): K == 0 with peer buffers is not supported")
+        return y
+    c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+    return _run_scaled_mm(c, mat2, scale_a, scale_b, scale_result, bool(use_fast_accum), y=y, peers=tuple(peers))
 
 
 def scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_dtype=None, use_fast_accum=False,

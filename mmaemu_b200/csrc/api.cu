@@ -43,7 +43,10 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
         int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme, const float* sa, const float* sb,
         const float* sr, int epilogue, int patch, int kernel, void* stream, void* workspace = nullptr,
         size_t workspace_bytes = 0, const void* a_hp = nullptr, int64_t ld_hp = 0, int hp_dtype = 0,
-        const float* quant_scale = nullptr) {
+        const float* quant_scale = nullptr, void* const* peer_D = nullptr, int n_peers = 0) {
+  if (n_peers < 0 || n_peers > MMB200_MAX_PEERS || (n_peers > 0 && !peer_D)) return MMB200_ERR_BAD_ARG;
+  for (int q = 0; q < n_peers; ++q)
+    if (!peer_D[q]) return MMB200_ERR_BAD_ARG;
   if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
   if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
   if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
@@ -79,6 +82,8 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   p.scheme = S > 1 ? scheme : MMB200_SCHEME_NONE;
   p.epilogue = epilogue;
   p.patch_nonfinite = patch;
+  p.n_peers = n_peers;
+  for (int q = 0; q < n_peers; ++q) p.peer_D[q] = peer_D[q];
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t err;
@@ -143,6 +148,35 @@ size_t out_size(int out_dtype) {
   return out_dtype == MMB200_OUT_F32 ? 4 : (out_dtype <= MMB200_OUT_F16 ? 2 : 1);
 }
 
+// Issue-rate probe: every thread runs `iters` rounds of 32 independent dependent-chain steps of one instruction kind
+// (0: fma.rz.f32, 1: a three-input integer add and a three-input logic operation alternating), so that a launch with
+// enough warps per SM is bound by the issue rate of that instruction's pipe. The result is stored so that nothing is
+// optimised away.
+template <int KIND>
+__global__ void __launch_bounds__(256) probe_kernel(int iters, float* sink) {
+  float f[32];
+  uint32_t u[32];
+#pragma unroll
+  for (int q = 0; q < 32; ++q) {
+    f[q] = 1.0f + (float)(threadIdx.x + q) * 1e-3f;
+    u[q] = threadIdx.x * 2654435761u + q;
+  }
+  const float m = 1.0f + 1e-7f * (float)blockIdx.x, c = 1e-9f;
+  const uint32_t k1 = blockIdx.x | 1u, k2 = threadIdx.x;
+#pragma unroll 1
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      if (KIND == 0) f[q] = __fmaf_rz(f[q], m, c);
+      else u[q] = (q & 1) ? (u[q] + k1 + k2) : ((u[q] & k1) ^ k2);
+    }
+  }
+  float acc = 0.0f;
+#pragma unroll
+  for (int q = 0; q < 32; ++q) acc += KIND == 0 ? f[q] : (float)u[q];
+  sink[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
+}
+
 }  // namespace
 
 int mmb::record_cuda_error(cudaError_t err) { return cuda_fail(err); }
@@ -205,6 +239,17 @@ int mmb200_workspace_status(const void* workspace, int M, int N, int K, int S, v
   return read_status(workspace, M, N, K, S, static_cast<cudaStream_t>(stream));
 }
 
+int mmb200_probe_issue_rate(int kind, int ctas, int iters, float* sink, void* stream) {
+  if ((kind != 0 && kind != 1) || ctas <= 0 || iters <= 0 || !sink) return MMB200_ERR_BAD_ARG;
+  int rc = current_device_ok();
+  if (rc != MMB200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kind == 0) probe_kernel<0><<<ctas, 256, 0, st>>>(iters, sink);
+  else probe_kernel<1><<<ctas, 256, 0, st>>>(iters, sink);
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? MMB200_OK : cuda_fail(err);
+}
+
 void mmb200_test_hooks(int wait_polls, int announce_extra_bytes) { mmb::staged_test_hooks(wait_polls, announce_extra_bytes); }
 
 size_t mmb200_workspace_bytes(int M, int N, int K) { return mmb::staged_workspace_bytes(M, N, K, 1, false); }
@@ -217,6 +262,15 @@ int mmb200_scaled_mm_ws(const void* A, int64_t lda, int fmt_a, const void* B, in
   if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
   return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
              scale_result, 1, 1, kernel, stream, workspace, workspace_bytes);
+}
+
+int mmb200_scaled_mm_peers(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int fmt_b, void* D,
+                           int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme,
+                           const float* scale_a, const float* scale_b, const float* scale_result, int kernel,
+                           void* workspace, size_t workspace_bytes, void* const* peer_D, int n_peers, void* stream) {
+  if (!scale_a || !scale_b) return MMB200_ERR_BAD_ARG;
+  return run(A, lda, fmt_a, B, ldb, fmt_b, D, ldd, out_dtype, M, N, K, nfma, fast, S, scheme, scale_a, scale_b,
+             scale_result, 1, 1, kernel, stream, workspace, workspace_bytes, nullptr, 0, 0, nullptr, peer_D, n_peers);
 }
 
 int mmb200_quantize_scaled_mm_ws(const void* X, int64_t ldx, int x_dtype, const float* quant_scale, void* A_codes,

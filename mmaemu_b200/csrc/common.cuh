@@ -42,6 +42,10 @@ struct Params {
   int* status;
   int k_tiles;
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
+  // multi-GPU assembly: the same output element is also stored at the same index of every peer_D[i] (device pointers
+  // into other GPUs' memory, mapped into this process), so that every GPU ends up with the whole result
+  void* peer_D[MMB200_MAX_PEERS];
+  int n_peers;
   int wait_polls;        // bound of every wait on an mbarrier in the staged kernels, in polls of up to ~1 us each
   int test_announce_extra;  // test hook: bytes the issuing thread announces beyond what it copies (the wait then runs out)
   // quantise prologue (staged kernels, operand A in E4M3 only): when a_hp is set, the pre-decode pass reads M x K
@@ -164,7 +168,8 @@ __device__ __forceinline__ uint8_t f32_to_fp8_bits(float f, int fmt) {
 
 struct Epilogue {
   float alpha, scale_result;
-  int has_scale_result, out_dtype, enabled;
+  int has_scale_result, out_dtype, enabled, n_peers;
+  void* const* peers;
   __device__ __forceinline__ void init(const Params& p) {
     enabled = p.epilogue;
     out_dtype = p.out_dtype;
@@ -172,12 +177,21 @@ struct Epilogue {
     alpha = __fmul_rn(sa, sb);
     has_scale_result = p.scale_result != nullptr;
     scale_result = has_scale_result ? *p.scale_result : 1.0f;
+    n_peers = p.n_peers;
+    peers = p.peer_D;
+  }
+  // One element of the output dtype at index idx of D and of every peer's buffer (plain stores; the peers' copies
+  // become visible to their GPUs with the synchronisation that follows the kernel).
+  template <typename T>
+  __device__ __forceinline__ void put(void* D, long long idx, T bits) const {
+    reinterpret_cast<T*>(D)[idx] = bits;
+    for (int q = 0; q < n_peers; ++q) reinterpret_cast<T*>(peers[q])[idx] = bits;
   }
   __device__ __forceinline__ void store(void* D, long long idx, float acc) const {
     if (!enabled) {
       uint32_t u = __float_as_uint(acc);
       if ((u & 0x7FFFFFFFu) > 0x7F800000u) u = CANON_NAN32;
-      reinterpret_cast<uint32_t*>(D)[idx] = u;
+      put<uint32_t>(D, idx, u);
       return;
     }
     float y = __fmaf_rn(acc, alpha, 0.0f);
@@ -185,15 +199,14 @@ struct Epilogue {
       case MMB200_OUT_F32: {
         uint32_t u = __float_as_uint(y);
         if ((u & 0x7FFFFFFFu) > 0x7F800000u) u = CANON_NAN32;
-        reinterpret_cast<uint32_t*>(D)[idx] = u;
+        put<uint32_t>(D, idx, u);
         break;
       }
-      case MMB200_OUT_BF16: reinterpret_cast<uint16_t*>(D)[idx] = f32_to_bf16_bits(y); break;
-      case MMB200_OUT_F16: reinterpret_cast<uint16_t*>(D)[idx] = f32_to_f16_bits(y); break;
+      case MMB200_OUT_BF16: put<uint16_t>(D, idx, f32_to_bf16_bits(y)); break;
+      case MMB200_OUT_F16: put<uint16_t>(D, idx, f32_to_f16_bits(y)); break;
       default:
         if (has_scale_result) y = __fmul_rn(y, scale_result);
-        reinterpret_cast<uint8_t*>(D)[idx] =
-            f32_to_fp8_bits(y, out_dtype == MMB200_OUT_E4M3 ? MMB200_FMT_E4M3 : MMB200_FMT_E5M2);
+        put<uint8_t>(D, idx, f32_to_fp8_bits(y, out_dtype == MMB200_OUT_E4M3 ? MMB200_FMT_E4M3 : MMB200_FMT_E5M2));
     }
   }
 };

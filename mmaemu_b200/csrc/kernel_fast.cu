@@ -107,7 +107,7 @@ __device__ __forceinline__ uint32_t decode16(const uint4 raw, Tile& tile, int ro
 #define MMB_STRIPS 2
 #endif
 #ifndef MMB_GROUP_UNROLL
-#define MMB_GROUP_UNROLL 2
+#define MMB_GROUP_UNROLL 1
 #endif
 constexpr int STRIPS = MMB_STRIPS, NJ = TN / STRIPS, GROUP_UNROLL = MMB_GROUP_UNROLL;
 static_assert(STRIPS == 1 || STRIPS == 2, "one or two column strips");

@@ -52,7 +52,8 @@ def _worker(rank, world, port, M, N, K, profile, out_name, local, q):
                                 fmt_a="e5m2", fmt_b="e4m3", preset=profile, fast=True, S=d.S, scheme=d.scheme)
         it = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[y.element_size()]
         got = y.contiguous().view(it).numpy().view(want.dtype)
-        ok = y.shape == (M, N) and np.array_equal(got, want) and seen == [1 if d.S == 1 else (d.S, d.scheme)]
+        called = [] if m1 == m0 else [1 if d.S == 1 else (d.S, d.scheme)]     # a rank without rows computes nothing
+        ok = y.shape == (M, N) and np.array_equal(got, want) and seen == called
         q.put((rank, bool(ok), d.S))
         dist.barrier()
     finally:
@@ -96,6 +97,71 @@ def test_two_ranks_assemble_the_oracle_result(M, N, K, profile, out, local):
         p.start()
     for p in procs:
         p.join(300)
+        assert p.exitcode == 0
+    results = sorted(q.get(timeout=5) for _ in range(2))
+    assert [r[1] for r in results] == [True, True], results
+
+
+def _worker_reject(rank, world, port, case, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    import torch.distributed as dist
+    import mmaemu_b200 as mm
+    from mmaemu_b200.sharding import shard_rows, sharded_scaled_mm
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        M, N, K = 100, 64, 256                              # rank 1 owns no rows
+        g = torch.Generator().manual_seed(5)
+        a = (torch.randn(M, K, generator=g) * 4).to(F8["e4m3"])
+        bt = (torch.randn(N, K, generator=g) * 4).to(F8["e4m3"])
+        sa, sb = torch.tensor(0.5), torch.tensor(2.0)
+        kw = dict(out_dtype=torch.bfloat16, profile="ada", compute=_oracle_compute([]))
+        want = None
+        if case == "bias":
+            kw["bias"] = torch.zeros(N, dtype=torch.bfloat16)
+            want = mm.UnsupportedFeatureError
+        elif case == "rowwise":
+            sa, sb = torch.full((M, 1), 0.5), torch.full((1, N), 2.0)
+            want = mm.UnsupportedFeatureError
+        elif case == "grad":
+            sa = sa.clone().requires_grad_(True)
+            want = mm.UnsupportedFeatureError
+        elif case == "e5m2_out":
+            kw["out_dtype"] = torch.float8_e5m2           # e4m3 x e4m3 -> e5m2: the profile rejects it
+            want = mm.ReferenceRejectsError
+        elif case == "layout":
+            bt = bt.t().contiguous().t()                    # mat2 = bt.t() is then row-major: cuBLASLt rejects
+            want = mm.ReferenceRejectsError
+        m0, m1 = shard_rows(M, world, rank)
+        local = case != "bias"                              # both ways of passing the operand
+        try:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                if local:
+                    sharded_scaled_mm(a[m0:m1], bt.t(), sa, sb, input_is_local=True, full_rows=M, **kw)
+                else:
+                    sharded_scaled_mm(a, bt.t(), sa, sb, **kw)
+            raised = None
+        except Exception as e:  # noqa: BLE001
+            raised = type(e)
+        q.put((rank, raised is want, str(raised)))
+        dist.barrier()                                      # reached by every rank: nobody is stuck in a collective
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["bias", "rowwise", "grad", "e5m2_out", "layout"])
+def test_a_rejected_call_is_rejected_on_every_rank(case):
+    """The whole call is validated from metadata before any rank computes, so a rank that owns no rows raises the same
+    exception as the others instead of walking into the collective alone."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_reject, args=(r, 2, port, case, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
         assert p.exitcode == 0
     results = sorted(q.get(timeout=5) for _ in range(2))
     assert [r[1] for r in results] == [True, True], results
