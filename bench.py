@@ -345,21 +345,28 @@ class Timer:
 
 def issue_peak(L, timer, clk_mhz):
     """Peak of the roofline: lane-instructions per second the SMs issue. Measured live with the library's probe kernel
-    (independent round-toward-zero FMAs, 1024 threads per SM) and, beside it, the nominal 148 SMs x 128 lanes x clock."""
+    (independent round-toward-zero FMAs, 2048 threads per SM) and, beside it, the nominal 148 SMs x 128 lanes x clock
+    and the rate of the integer pipe (three-input adds and logic operations) from the same probe."""
     import torch
     nominal = 148 * 128 * clk_mhz * 1e6 / 1e12
+    info = {"nominal_fp32_lanes": nominal}
     try:
         iters, ctas = 4096, 148 * 8
         stream = ctypes.c_void_p(timer.stream.cuda_stream)
         sink = torch.zeros(ctas * 256, dtype=torch.float32, device=timer.dev)
-        run = lambda: L.mmb200_probe_issue_rate(0, ctas, iters, sink.data_ptr(), stream)  # noqa: E731
-        if run() != 0:
-            return nominal, {"nominal": nominal, "measured": None}
-        ms = timer.median_ms(run, 5)
-        ops = float(ctas) * 256 * iters * 32            # 32 independent FMAs per thread and iteration
-        return ops / (ms / 1e3) / 1e12, {"nominal": nominal, "measured_ffma_rz": ops / (ms / 1e3) / 1e12, "probe_ms": ms}
+        ops = float(ctas) * 256 * iters * 32            # 32 independent instructions per thread and iteration
+        rates = {}
+        for kind, name in ((0, "measured_ffma_rz"), (1, "measured_iadd3_lop3")):
+            run = lambda: L.mmb200_probe_issue_rate(kind, ctas, iters, sink.data_ptr(), stream)  # noqa: E731
+            if run() != 0:
+                return nominal, info
+            ms = timer.median_ms(run, 5)
+            rates[name] = ops / (ms / 1e3) / 1e12
+            info[name] = rates[name]
+            info[name + "_lanes_per_clk_sm"] = rates[name] * 1e12 / (148 * clk_mhz * 1e6)
+        return rates["measured_ffma_rz"], info
     except Exception:  # noqa: BLE001
-        return nominal, {"nominal": nominal, "measured": None}
+        return nominal, info
 
 
 def sampled_gate(mm, oracle, y, a_u8, bt_u8, sa, sb, cfg, S, scheme, label, rows=None, cols=None):
@@ -515,13 +522,17 @@ def run_one_gpu(args) -> int:
         cfg["fast"] = True
     if args.profile:
         cfg["profile"] = args.profile
+    if args.formats:
+        cfg.update(fa=args.formats[0], fb=args.formats[1], name="custom")
+    if args.out:
+        cfg.update(out=args.out, name="custom")
     default_workload = cfg == HEADLINE
     kernel = args.kernel
     backend = "cuda:b200" if kernel == "auto" else f"cuda:b200-{kernel}"
     if default_workload:
         a, bt, sa, sb = headline_operands()
     else:
-        a, bt = gaussian_codes(cfg["M"], cfg["K"], 4.0, 2), gaussian_codes(cfg["N"], cfg["K"], 4.0, 3)
+        a, bt = gaussian_codes(cfg["M"], cfg["K"], 4.0, 2, cfg["fa"]), gaussian_codes(cfg["N"], cfg["K"], 4.0, 3, cfg["fb"])
         sa, sb = torch.tensor(0.37), torch.tensor(1.9)
     M, N, K = cfg["M"], cfg["N"], cfg["K"]
     od = getattr(torch, cfg["out"])
@@ -796,6 +807,9 @@ def main() -> int:
     ap.add_argument("--kernel", choices=("auto", "integer", "fast"), default="auto")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="problem size instead of the headline 4096 4096 4096 (profiling runs, one GPU)")
+    ap.add_argument("--formats", nargs=2, choices=("e4m3", "e5m2"), metavar=("A", "B"), default=None,
+                    help="FP8 formats of the two operands instead of e4m3 e4m3 (profiling runs, one GPU)")
+    ap.add_argument("--out", choices=("float32", "bfloat16", "float16"), default=None, help="output dtype (profiling runs)")
     ap.add_argument("--fast-accum", action="store_true", help="use_fast_accum=True instead of torch's default")
     ap.add_argument("--profile", default=None, help="emulated platform profile (default hopper)")
     ap.add_argument("--skip-gate", action="store_true", help="skip the exactness gate before timing")

@@ -409,8 +409,8 @@ def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=Non
     scale_a = 1 / quant_scale). x: [M, K] fp32 or bf16, unit stride along K; quant_scale: one-element fp32 tensor
     (with bf16 activations torch's type promotion rounds it to bf16 before the multiplication, and so does this call).
     Everything else, including every check and raise, is scaled_mm's, applied to the E4M3 tensor the call produces.
-    Returns y, or (y, xq) with return_codes=True. Activations whose rows are not 16-byte aligned are quantised by the
-    torch expression above and multiplied by a plain scaled_mm call."""
+    Returns y, or (y, xq) with return_codes=True. Activations or weights that the decode pass cannot read with 16-byte
+    loads raise ValueError (there is no path through torch operations)."""
     if not isinstance(x, torch.Tensor) or x.dtype not in (torch.float32, torch.bfloat16) or x.dim() != 2:
         raise TypeError("quantized_scaled_mm(): x must be a 2-D fp32 or bf16 tensor")
     if not isinstance(quant_scale, torch.Tensor) or quant_scale.numel() != 1 or quant_scale.dtype != torch.float32:
@@ -432,10 +432,15 @@ def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=Non
         bt = mat2.detach().t()
         ldb = bt.stride(0) if c.N > 1 else c.K
         fused = bt.data_ptr() % 16 == 0 and ldb % 16 == 0
-    if not fused:
-        xq.copy_((xs * quant_scale.to(xs.device)).clamp(-448, 448).to(torch.float8_e4m3fn))
+    if not fused and not c.early:
+        raise ValueError("quantized_scaled_mm(): the quantisation runs inside the kernels' decode pass, which reads x and "
+                         "mat2 with 16-byte loads and needs scratch memory: x must have unit stride along K, 16-byte "
+                         "aligned rows (base address and row stride), mat2.t() must be 16-byte aligned with a leading "
+                         "dimension that is a multiple of 16, and MMAEMU_B200_WORKSPACE must not be 0. Quantise with "
+                         "torch and call scaled_mm for other layouts.")
+    if c.early:
         y = scaled_mm(xq, mat2, scale_a, scale_b, None, scale_result, out_dtype, use_fast_accum, profile=profile,
-                      splitk=splitk)
+                      splitk=splitk)                     # zero-size result: nothing to quantise or compute
         return (y, xq) if return_codes else y
     y = torch.empty((c.M, c.N), dtype=c.od, device=dev)
     keep_q, pq = _scalar_ptr(quant_scale, dev)

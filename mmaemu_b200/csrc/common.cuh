@@ -125,6 +125,16 @@ __device__ inline bool nonfinite_value(const uint8_t* __restrict__ a, const uint
   return false;
 }
 
+// The same from the class flags of the output's row and column (bit 0: a NaN code was seen, bit 1: an infinity): a NaN
+// code anywhere in the row or the column makes the sum NaN whatever it is multiplied with, so only outputs whose row or
+// column holds infinities and no NaN need the walk over K. Returns false when the sum is finite.
+__device__ __forceinline__ bool nonfinite_patch(int flags, const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
+                                                int K, int fmt_a, int fmt_b, uint32_t& bits) {
+  if (flags & 1) { bits = CANON_NAN32; return true; }
+  if (flags & 2) return nonfinite_value(a, b, K, fmt_a, fmt_b, bits);
+  return false;
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Epilogue: y = RN32(fma(acc, alpha, +0)) with alpha = RN32(scale_a * scale_b); conversion to the output dtype with
 // a second rounding; fp8 outputs: optional RN32(y * scale_result), saturation to +-448 / +-57344 (Inf included, NaN
@@ -180,33 +190,75 @@ struct Epilogue {
     n_peers = p.n_peers;
     peers = p.peer_D;
   }
-  // One element of the output dtype at index idx of D and of every peer's buffer (plain stores; the peers' copies
-  // become visible to their GPUs with the synchronisation that follows the kernel).
-  template <typename T>
-  __device__ __forceinline__ void put(void* D, long long idx, T bits) const {
-    reinterpret_cast<T*>(D)[idx] = bits;
-    for (int q = 0; q < n_peers; ++q) reinterpret_cast<T*>(peers[q])[idx] = bits;
+  __device__ __forceinline__ int elem_size() const {
+    return (!enabled || out_dtype == MMB200_OUT_F32) ? 4 : (out_dtype <= MMB200_OUT_F16 ? 2 : 1);
   }
-  __device__ __forceinline__ void store(void* D, long long idx, float acc) const {
+  // Bit pattern of one output element (in the low bits of the result) for an accumulator value.
+  __device__ __forceinline__ uint32_t bits_of(float acc) const {
     if (!enabled) {
-      uint32_t u = __float_as_uint(acc);
-      if ((u & 0x7FFFFFFFu) > 0x7F800000u) u = CANON_NAN32;
-      put<uint32_t>(D, idx, u);
-      return;
+      const uint32_t u = __float_as_uint(acc);
+      return (u & 0x7FFFFFFFu) > 0x7F800000u ? CANON_NAN32 : u;
     }
     float y = __fmaf_rn(acc, alpha, 0.0f);
     switch (out_dtype) {
       case MMB200_OUT_F32: {
-        uint32_t u = __float_as_uint(y);
-        if ((u & 0x7FFFFFFFu) > 0x7F800000u) u = CANON_NAN32;
-        put<uint32_t>(D, idx, u);
-        break;
+        const uint32_t u = __float_as_uint(y);
+        return (u & 0x7FFFFFFFu) > 0x7F800000u ? CANON_NAN32 : u;
       }
-      case MMB200_OUT_BF16: put<uint16_t>(D, idx, f32_to_bf16_bits(y)); break;
-      case MMB200_OUT_F16: put<uint16_t>(D, idx, f32_to_f16_bits(y)); break;
+      case MMB200_OUT_BF16: return f32_to_bf16_bits(y);
+      case MMB200_OUT_F16: return f32_to_f16_bits(y);
       default:
         if (has_scale_result) y = __fmul_rn(y, scale_result);
-        put<uint8_t>(D, idx, f32_to_fp8_bits(y, out_dtype == MMB200_OUT_E4M3 ? MMB200_FMT_E4M3 : MMB200_FMT_E5M2));
+        return f32_to_fp8_bits(y, out_dtype == MMB200_OUT_E4M3 ? MMB200_FMT_E4M3 : MMB200_FMT_E5M2);
+    }
+  }
+  // One element at index idx of D and of every peer's buffer (plain stores; the peers' copies become visible to their
+  // GPUs with the synchronisation that follows the kernel).
+  __device__ __forceinline__ void store(void* D, long long idx, float acc) const {
+    const uint32_t b = bits_of(acc);
+    const int es = elem_size();
+    for (int q = -1; q < n_peers; ++q) {
+      void* dst = q < 0 ? D : peers[q];
+      if (es == 4) reinterpret_cast<uint32_t*>(dst)[idx] = b;
+      else if (es == 2) reinterpret_cast<uint16_t*>(dst)[idx] = (uint16_t)b;
+      else reinterpret_cast<uint8_t*>(dst)[idx] = (uint8_t)b;
+    }
+  }
+  // Tile-wise output for the 128 x 128 kernels: every thread parks the elements it owns in a shared-memory image of the
+  // CTA's output tile (rows of 128 elements, 16 bytes of padding per row), then the whole CTA writes the image out in
+  // 16-byte pieces of whole rows -- to D and to every peer's buffer -- so that the stores are full 32-byte sectors
+  // locally and large packets over NVLink instead of 2-byte scattered ones.
+  static constexpr int TILE_DIM = 128;
+  __device__ __forceinline__ int tile_pitch() const { return TILE_DIM * elem_size() + 16; }
+  __device__ __forceinline__ void park(unsigned char* tile, int lr, int lc, float acc) const {
+    const uint32_t b = bits_of(acc);
+    const int es = elem_size();
+    unsigned char* dst = tile + lr * tile_pitch() + lc * es;
+    if (es == 4) *reinterpret_cast<uint32_t*>(dst) = b;
+    else if (es == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)b;
+    else *dst = (uint8_t)b;
+  }
+  __device__ __forceinline__ void flush(const Params& p, const unsigned char* tile, int m0, int n0, int tid,
+                                        int nthreads) const {
+    const int es = elem_size(), pitch = tile_pitch(), per_row = TILE_DIM * es / 16, per_piece = 16 / es;
+    bool vec = (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && ((p.ldd * es) % 16 == 0);
+    for (int q = 0; q < n_peers; ++q) vec = vec && (reinterpret_cast<uintptr_t>(peers[q]) % 16 == 0);
+    for (int idx = tid; idx < TILE_DIM * per_row; idx += nthreads) {
+      const int row = idx / per_row, piece = idx % per_row, gm = m0 + row, gn = n0 + piece * per_piece;
+      if (gm >= p.M || gn >= p.N) continue;
+      const unsigned char* src = tile + row * pitch + piece * 16;
+      const long long off = ((long long)gm * p.ldd + gn) * es;
+      if (vec && gn + per_piece <= p.N) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        for (int q = -1; q < n_peers; ++q)
+          *reinterpret_cast<uint4*>(static_cast<unsigned char*>(q < 0 ? p.D : peers[q]) + off) = v;
+      } else {
+        const int bytes = min(per_piece, p.N - gn) * es;
+        for (int q = -1; q < n_peers; ++q) {
+          unsigned char* dst = static_cast<unsigned char*>(q < 0 ? p.D : peers[q]) + off;
+          for (int e = 0; e < bytes; ++e) dst[e] = src[e];
+        }
+      }
     }
   }
 };

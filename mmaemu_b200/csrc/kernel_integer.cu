@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) integer_kernel(const __grid_constant_
       float v = tot[i][j];
       if (p.patch_nonfinite && (sm.flag_a[tm * TM + i] | sm.flag_b[tn * TN + j])) {
         uint32_t bits;
-        if (nonfinite_value(p.A + (long long)gm * p.lda, p.B + (long long)gn * p.ldb, p.K, p.fmt_a, p.fmt_b, bits))
+        if (nonfinite_patch(sm.flag_a[tm * TM + i] | sm.flag_b[tn * TN + j], p.A + (long long)gm * p.lda, p.B + (long long)gn * p.ldb, p.K, p.fmt_a, p.fmt_b, bits))
           v = __uint_as_float(bits);
       }
       epi.store(p.D, (long long)gm * p.ldd + gn, v);

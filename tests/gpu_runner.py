@@ -29,10 +29,12 @@ def _dev(x):
 
 
 def _ws(L, M, N, K, kernel, S=1):
-    """Scratch memory for the staged kernels when `kernel` is 'staged' or 'staged-whole' (test-side names: automatic
-    choice + workspace; '-whole' turns K slicing off, so that few-tile shapes run the one-pass plan walkers)."""
+    """Scratch memory for the staged kernels when `kernel` is 'staged', 'staged-whole' or 'staged-int' (test-side
+    names: automatic choice + workspace; '-whole' turns K slicing off, so that few-tile shapes run the one-pass plan
+    walkers; '-int' keeps the exponent pass of E4M3 x E4M3 on the CUDA cores instead of the tensor cores)."""
     os.environ["MMAEMU_B200_SLICES"] = "0" if kernel == "staged-whole" else "1"
-    if kernel not in ("staged", "staged-whole"):
+    os.environ["MMAEMU_B200_TC_EPASS"] = "0" if kernel == "staged-int" else "1"
+    if kernel not in ("staged", "staged-whole", "staged-int"):
         return None, None, 0, kernel
     n = int(L.mmb200_workspace_bytes_split(M, N, K, S))
     ws = torch.empty(max(n, 1), dtype=torch.uint8, device=DEV)
@@ -79,11 +81,11 @@ def accumulate(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=True, S=1, s
 
 
 def chain(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, kernel="auto"):
-    if kernel in ("staged", "staged-whole"):     # the chain entry point has no workspace variant: fast plan, no patch
+    if kernel in ("staged", "staged-whole", "staged-int"):     # the chain entry point has no workspace variant: fast plan, no patch
         clean = [np.where((x & 0x7F) == 0x7F, 0, x) if f == "e4m3" else np.where((x & 0x7C) == 0x7C, 0, x)
                  for x, f in ((a, fmt_a), (b, fmt_b))]
         return accumulate(clean[0].astype(np.uint8), clean[1].astype(np.uint8), fmt_a=fmt_a, fmt_b=fmt_b, preset=preset,
-                          fast=True, kernel="staged")
+                          fast=True, kernel=kernel)
     L = _lib.load()
     M, K = a.shape
     N = b.shape[0]

@@ -218,7 +218,7 @@ def test_call_is_capturable_in_a_cuda_graph():
 def test_quantised_activations(dtype):
     """quantized_scaled_mm: the E4M3 codes equal torch's (x * s).clamp(-448, 448).to(float8_e4m3fn) on the device, and
     the product equals scaled_mm on those codes (checked against the oracle), for contiguous and padded activations,
-    an unsplit and a split plan, and the unfused fallback (rows that are not 16-byte aligned)."""
+    an unsplit and a split plan; rows that are not 16-byte aligned are refused (no path through torch operations)."""
     rng = np.random.default_rng(31)
     for (M, N, K, pad, profile, split) in ((200, 192, 1024, 0, "hopper-te", 1), (64, 128, 2048, 24, "ada", (4, "serial")),
                                            (33, 48, 1008, 3, "hopper", 1)):
@@ -231,6 +231,10 @@ def test_quantised_activations(dtype):
         w = datagen._round_to(rng.standard_normal((N, K)) * 0.02 * 448 / 0.08, "e4m3")
         tw = torch.from_numpy(w).to(DEV).view(F8["e4m3"])
         sa, sb = (1.0 / qs).to(torch.float32), torch.tensor(0.08 / 448, device=DEV)
+        if pad % (4 if dtype == torch.float32 else 8):
+            with pytest.raises(ValueError, match="16-byte"):
+                mm.quantized_scaled_mm(xt, qs, tw.t(), sa, sb, out_dtype=torch.bfloat16, profile=profile, splitk=split)
+            continue
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
             y, xq = mm.quantized_scaled_mm(xt, qs, tw.t(), sa, sb, out_dtype=torch.bfloat16, profile=profile,
@@ -255,6 +259,12 @@ def test_quantised_activations_argument_checks():
         mm.quantized_scaled_mm(x, 2.0, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1)
     with pytest.raises(mm.SplitKUnknownError):                      # scaled_mm's own checks apply to the produced tensor
         mm.quantized_scaled_mm(x, one, w.t(), one, one, out_dtype=torch.bfloat16, profile="hopper")
+    # rows that the decode pass cannot read with 16-byte loads: refused, never computed by torch operations instead
+    wide = torch.zeros(16, 34, device=DEV)
+    with pytest.raises(ValueError, match="16-byte"):
+        mm.quantized_scaled_mm(wide[:, 1:33], one, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1, profile="ada")
+    empty = mm.quantized_scaled_mm(x[:0], one, w.t(), one, one, out_dtype=torch.bfloat16, splitk=1, profile="ada")
+    assert empty.shape == (0, 16)
 
 
 def test_a_wait_that_runs_out_is_reported_and_nothing_is_written():

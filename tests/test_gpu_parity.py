@@ -67,6 +67,24 @@ def test_conformance_matrix(gpu, cls, fmts, preset, kernel):
                   f"{cls} {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("preset", (16, 32))
+@pytest.mark.parametrize("cls", datagen.CLASSES)
+def test_packed_integer_exponent_pass_for_e4m3_pairs(gpu, cls, preset):
+    """E4M3 x E4M3 takes its exponent pass from the tensor cores by default; the packed-integer pass of the other format
+    pairs serves it too (MMAEMU_B200_TC_EPASS=0) and must give the same bits: chains, a slow-accumulation plan and a
+    split plan."""
+    rng = np.random.default_rng(zlib.crc32(repr((cls, preset, "int")).encode()))
+    for M, N, K in ((65, 63, 48), (200, 257, 1920)):
+        a = datagen.codes(rng, M, K, "e4m3", cls, 0)
+        b = datagen.codes(rng, N, K, "e4m3", cls, 1)
+        _same(gpu.chain(a, b, preset=preset, kernel="staged-int"), oracle.accumulate(a, b, preset=preset, fast=True),
+              f"{cls} {M}x{N}x{K}")
+        sch = "contiguous" if preset == 32 else "pairwise"
+        for kw in (dict(fast=False, S=1, scheme="none"), dict(fast=True, S=3, scheme=sch)):
+            _same(gpu.accumulate(a, b, preset=preset, kernel="staged-int", **kw), oracle.accumulate(a, b, preset=preset, **kw),
+                  f"{cls} {M}x{N}x{K} {kw}")
+
+
 PLANS = ([(16, False, 1, "none"), (32, False, 1, "none")]
          + [(16, f, S, sch) for sch in ("serial", "pairwise") for S in (2, 3, 8, 12, 29) for f in (True, False)]
          + [(32, f, S, "contiguous") for S in (2, 3, 4, 5, 6, 7, 8, 24) for f in (True, False)]

@@ -13,6 +13,7 @@ import torch
 
 import datagen
 from mmaemu_b200 import _lib
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -50,12 +51,19 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
     a2[3, 17], a2[150, 0], b2[7, 99] = 0x7E, 0xFC, 0x7F
     first = ("e4m3", "e4m3", "bfloat16", 32, False, [0.37, 1.5, 1.0])
     second = ("e5m2", "e4m3", "float8_e4m3fn", 16, True, [0.011, 2.0, 0.75])
+    L = _lib.load()
     for a, b, cfg in ((a1, b1, first), (a2, b2, second)):
         rc, got = call("static", a, b, *cfg)
         _lib.check("mmb200_scaled_mm_static", rc)
         rc, want = call("regular", a, b, *cfg)
         _lib.check("mmb200_scaled_mm", rc)
         assert np.array_equal(got, want), f"{int((got != want).sum())} of {want.size} outputs differ"
+        fa, fb, out, nfma, fast, sc = cfg
+        truth = oracle.scaled_mm(a, b, sc[0], sc[1], out=out, fmt_a=fa, fmt_b=fb, preset=nfma, fast=fast,
+                                 scale_result=sc[2] if out.startswith("float8") else None)
+        assert np.array_equal(got.view(truth.dtype), truth), "the two GPU entry points agree with each other but not " \
+                                                             "with the oracle"
+        assert L.mmb200_scaled_mm_static_status(a.shape[0], b.shape[0], a.shape[1], None) == _lib.OK
 
 
 def test_static_scratch_entry_point_refuses_what_it_cannot_serve():
