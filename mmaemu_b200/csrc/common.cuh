@@ -60,6 +60,8 @@ struct Params {
   // running total and the pair slot of the split reduction (scratch memory)
   const uint32_t* ws_seq;
   int seq_len;
+  const uint32_t* ws_events;   // K slices: the sequence entries after which a chain or a split is complete, in order
+  int n_events;
   float* ws_tot;
   float* ws_slot;
   // K-sliced execution of plans with few output tiles (chains are independent of one another): slice y of the grid

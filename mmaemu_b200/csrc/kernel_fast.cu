@@ -451,8 +451,8 @@ __global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant_
   for (int q = 0; q < AHEAD; ++q) ahead[q] = q < p.n_chains ? src[(size_t)q * STRIDE] : 0.0f;
   int chain = 0;
 #pragma unroll 1
-  for (int e = 0; e < p.seq_len; ++e) {
-    const uint32_t entry = __ldg(p.ws_seq + e);
+  for (int e = 0; e < p.n_events; ++e) {
+    const uint32_t entry = __ldg(p.ws_events + e);
     if (seq_emits(entry, slow ? 1 : 0)) {
       last = ahead[0];
 #pragma unroll
@@ -484,8 +484,19 @@ __global__ void __launch_bounds__(THREADS) combine_kernel(const __grid_constant_
 }
 
 #if !defined(MMB_PART) || MMB_PART == 0
-__global__ void plan_sequence_kernel(Plan plan, int K, uint32_t* out) {
-  plan_sequence(plan, K, out, (int)threadIdx.x, (int)blockDim.x);
+// Writes the tile sequence and, behind it (`events`, when not null), the entries that matter to the second pass of
+// K-sliced execution in the same order: those after which a chain or a split is complete.
+__global__ void plan_sequence_kernel(Plan plan, int K, uint32_t* out, uint32_t* events) {
+  const int n = plan_sequence(plan, K, out, (int)threadIdx.x, (int)blockDim.x);
+  if (!events) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int m = 0;
+    for (int e = 0; e < n; ++e) {
+      const uint32_t entry = out[e];
+      if (seq_emits(entry, plan.group ? 1 : 0) || (entry & SEQ_SPLIT_END)) events[m++] = entry;
+    }
+  }
 }
 #endif
 
@@ -977,7 +988,8 @@ WorkspaceLayout workspace_layout(int M, int N, int K, int S, bool with_slices) {
   const bool sliceable = tiles < (size_t)SLICE_TILE_LIMIT;
   // the tile sequence (at most one entry per k-tile plus one per empty split): split plans and K slices
   w.tot = w.seq;
-  if (S > 1 || sliceable) w.tot = w.seq + (((size_t)w.k_tiles + (size_t)S + 8) * sizeof(uint32_t) + 255) / 256 * 256;
+  // (twice: the sequence, then the compact list of chain and split ends for the second pass of K slices)
+  if (S > 1 || sliceable) w.tot = w.seq + (2 * ((size_t)w.k_tiles + (size_t)S + 8) * sizeof(uint32_t) + 255) / 256 * 256;
   // split plans: the total and the pair slot of every output, [tile][output of the thread][thread]
   w.slot = w.tot + (S > 1 ? tiles * per_tile : 0);
   w.chains = w.slot + (S > 1 ? tiles * per_tile : 0);
@@ -1083,12 +1095,20 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
   if (err != cudaSuccess) return err;
   if (p.S > 1 || p.slices > 1) {
     p.seq_len = plan_sequence(plan, p.K, nullptr);
-    if ((size_t)p.seq_len * sizeof(uint32_t) > w.tot - w.seq) return cudaErrorInvalidValue;
+    if (2 * (size_t)p.seq_len * sizeof(uint32_t) > w.tot - w.seq) return cudaErrorInvalidValue;
     p.ws_seq = reinterpret_cast<const uint32_t*>(base + w.seq);
+    p.ws_events = nullptr;
+    p.n_events = 0;
+    if (p.slices > 1) {                      // the host holds the sequence when it slices: count the ends
+      for (uint32_t entry : seq)
+        p.n_events += (seq_emits(entry, plan.group ? 1 : 0) || (entry & SEQ_SPLIT_END)) ? 1 : 0;
+      p.ws_events = p.ws_seq + p.seq_len;
+    }
     p.ws_tot = reinterpret_cast<float*>(base + w.tot);
     p.ws_slot = reinterpret_cast<float*>(base + w.slot);
     p.ws_chains = reinterpret_cast<float*>(base + w.chains);
-    plan_sequence_kernel<<<1, THREADS, 0, stream>>>(plan, p.K, reinterpret_cast<uint32_t*>(base + w.seq));
+    plan_sequence_kernel<<<1, THREADS, 0, stream>>>(plan, p.K, reinterpret_cast<uint32_t*>(base + w.seq),
+                                                    const_cast<uint32_t*>(p.ws_events));
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     *launches += 1;
