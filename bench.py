@@ -682,8 +682,10 @@ def run_multi_gpu(args) -> int:
     bt_dev = strong_bt(dev).view(torch.float8_e4m3fn)
     sa_dev, sb_dev = torch.tensor(cfg["scale_a"], device=dev), torch.tensor(cfg["scale_b"], device=dev)
     timer = Timer(dev)
+    # keep_symmetric: the assembled result is used where the kernels put it (a symmetric-memory buffer that the next call
+    # of this shape reuses) instead of being copied out -- every output is still produced on every GPU in every step
     kw = dict(out_dtype=od, use_fast_accum=cfg["fast"], profile=cfg["profile"], splitk=cfg["splitk"],
-              input_is_local=True, full_rows=M, assemble=args.assemble)
+              input_is_local=True, full_rows=M, assemble=args.assemble, keep_symmetric=True)
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -783,7 +785,7 @@ def run_multi_gpu(args) -> int:
                        "profile": cfg["profile"], "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "multi_gpu": {"peer": "the kernel's epilogue stores each output into every GPU's copy of the "
                                              "result through peer pointers (symmetric memory, NVLink); a device-side "
-                                             "barrier before and after; the result is returned as a copy",
+                                             "barrier before and after; the result stays in that buffer (no copy)",
                                      "nccl": "row slabs + one NCCL all-gather per step"}[mode],
                        "n1_point": "the same problem on one GPU is `configs.cfg5_strong_n1` of the --gpus 1 line"},
             "compute_only_ms_per_step": compute_ms / args.steps,

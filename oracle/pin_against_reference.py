@@ -14,7 +14,7 @@ hard-coded hardware bytes in tests/test_api.py, and the unit tests of the plan l
 
 usage:  python oracle/pin_against_reference.py [--reference <checkout of astding/mmaemu>] [pytest args]
 Prints how many calls were served by the oracle and how many fell back to the reference's own code (custom presets,
-late-c presets, non-finite instruction-level operands), then pytest's summary. Exit code = pytest's.
+non-finite instruction-level operands), then pytest's summary. Exit code = pytest's.
 """
 from __future__ import annotations
 
@@ -48,10 +48,13 @@ class OraclePatch:
         from oracle import oracle
 
         def nfma_of(p):
-            """16 / 32 for the two characterised early-accumulator presets, else None (fall back)."""
+            """The oracle's preset code: 16 / 32 for the two early-accumulator presets, 288 for the late-accumulator
+            b200_mma_sync (32 products, 25 / 23 fraction bits); None (fall back) for anything else."""
             if isinstance(p, str):
                 p = presets._lookup(p)[0]
-            if p.late_c or p.frac != 13 or p.frac_out != 13 or p.nfma not in (16, 32):
+            if p.late_c:
+                return 288 if (p.nfma, p.frac, p.frac_out, p.min_exp) == (32, 25, 23, -133) else None
+            if p.frac != 13 or p.frac_out != 13 or p.nfma not in (16, 32):
                 return None
             return p.nfma
 
