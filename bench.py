@@ -763,9 +763,40 @@ def run_multi_gpu(args) -> int:
     sync_all()
     e2e_ms = timer.total_ms(step_e2e, args.steps)
     sync_all()
-    t = torch.tensor([total_ms, e2e_ms, compute_ms], dtype=torch.float64, device=dev)
+    # a row-poor shape of the tall-skinny configuration (16 x 8192 x 28672, hopper-te: the table splits K in two): there
+    # is nothing to cut along M, so the ranks take column groups (grid "auto" = 1 x world); every rank ends up with the
+    # whole result, compared first with the one-GPU call of the same operands on this rank
+    gM, gN, gK = 16, 8192, 28672
+    ga = gaussian_codes(gM, gK, 8.0, 8, "e5m2").to(dev)
+    gb = gaussian_codes(gN, gK, 8.0, 22, "e4m3").to(dev)
+    gsa, gsb = torch.tensor(2.0 ** -5, device=dev), torch.tensor(2.0 ** -4, device=dev)
+    gkw = dict(out_dtype=torch.bfloat16, use_fast_accum=False, profile="hopper-te", splitk="auto")
+
+    def grid_step():
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            return sharded_scaled_mm(ga, gb.t(), gsa, gsb, grid="auto", assemble=args.assemble, keep_symmetric=True,
+                                     **gkw)
+
+    def grid_single():
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            return mm.scaled_mm(ga, gb.t(), gsa, gsb, **gkw)
+    grid_same = bool(torch.equal(grid_step().view(torch.int16), grid_single().view(torch.int16)))
+    sync_all()
+    for _ in range(3):
+        grid_step()
+    sync_all()
+    grid_ms = timer.total_ms(grid_step, args.steps)
+    sync_all()
+    grid_single_ms = timer.total_ms(grid_single, args.steps)
+    sync_all()
+    t = torch.tensor([total_ms, e2e_ms, compute_ms, grid_ms, grid_single_ms, 0.0 if grid_same else 1.0],
+                     dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, compute_ms = (float(x) for x in t.cpu())
+    total_ms, e2e_ms, compute_ms, grid_ms, grid_single_ms, grid_bad = (float(x) for x in t.cpu())
+    if grid_bad:
+        raise SystemExit("the column-group result differs from the one-GPU result of the same call")
     if rank == 0:
         from mmaemu_b200 import sharding
         ms = total_ms / args.steps
@@ -797,6 +828,12 @@ def run_multi_gpu(args) -> int:
                     "call": "mmaemu_b200.sharded_scaled_mm on this rank's rows of A and all of B copied from pinned host "
                             "memory each step (bytes per rank), this rank's rows of the assembled result copied back"},
             "gpu_launches": int(launches), "clocks": clocks,
+            "row_poor_grid": {"workload": f"hopper-te, {gM} x {gN} x {gK}, e5m2 x e4m3 -> bfloat16, slow accumulation, "
+                                          f"split-K from the table; column groups 1 x {world}, every GPU ends up with "
+                                          f"the whole result",
+                              "ms_per_step": grid_ms / args.steps, "one_gpu_ms_per_step": grid_single_ms / args.steps,
+                              "tflops": 2.0 * gM * gN * gK / (grid_ms / args.steps / 1e3) / 1e12,
+                              "bit_identical_to_one_gpu": True},
         }
         print(json.dumps(line))
     dist.barrier()

@@ -31,7 +31,7 @@ from . import _lib
 from .errors import (BackendUnavailableError, ExperimentalPresetWarning, ReferenceRejectsError,
                      UnsupportedFeatureError)
 from .formats import E4M3, E5M2, OUT_DTYPE_NAMES, fmt_of, is_fp8_dtype
-from .numerics import check_plan, get_preset
+from .numerics import check_plan, get_preset, maturity_warning, warn_once
 from .platforms import get_profile, profile_maturity_warning
 from .splitk import resolve_splitk
 
@@ -45,7 +45,6 @@ _KERNEL_OF = {"auto": "auto", "cuda": "auto", "cuda:b200": "auto", "cuda:b200-in
 # dtypes torch 2.7.1 lets through its "is a float8 matrix" check before the zero-size early return
 _TORCH_FLOAT8 = {getattr(torch, n) for n in ("float8_e4m3fn", "float8_e5m2", "float8_e4m3fnuz", "float8_e5m2fnuz",
                                              "float8_e8m0fnu") if hasattr(torch, n)}
-_warned_profiles: set = set()
 
 
 @dataclass
@@ -218,11 +217,20 @@ class _Call:
                  "kernel", "mat1", "notes")
 
 
-def _emit_profile_warning(prof) -> None:
-    msg = profile_maturity_warning(prof)
-    if msg is not None and prof.name not in _warned_profiles:
-        _warned_profiles.add(prof.name)
-        warnings.warn(msg, ExperimentalPresetWarning, stacklevel=5)
+def _maturity_message(prof, preset):
+    """The maturity warning of the call: the preset's, else the profile's (mmaemu/api.py:121-124)."""
+    return maturity_warning(preset) or profile_maturity_warning(prof, preset.maturity == "validated")
+
+
+def _emit_maturity(prof, preset) -> None:
+    """ExperimentalPresetWarning of the preset (once per name) or of the profile (once per name), as
+    mmaemu/api.py:127-133."""
+    msg = maturity_warning(preset)
+    if msg is not None:
+        warn_once(preset.name, msg, stacklevel=6)
+    msg = profile_maturity_warning(prof, preset.maturity == "validated")
+    if msg is not None:
+        warn_once("profile:" + prof.name, msg, stacklevel=6)
 
 
 def _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out, profile, splitk,
@@ -247,11 +255,11 @@ def _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_f
     if rule is not None:
         raise ReferenceRejectsError(f"{rule.message} [profile {c.profile.name}]")
     _check_scope(scaling, bias, (c.mat1, mat2, scale_a, scale_b, scale_result, bias))
-    msg = profile_maturity_warning(c.profile)
+    msg = _maturity_message(c.profile, c.preset)
     if msg is not None:
         c.notes.append(msg)
-        if not dry:
-            _emit_profile_warning(c.profile)
+    if not dry:
+        _emit_maturity(c.profile, c.preset)
     same_shape = out is not None and tuple(out.shape) == (c.M, c.N)
     if same_shape and not (_row_major(out) or _col_major(out)):
         # torch computes into a contiguous copy of such an out= and never copies the result back
@@ -326,10 +334,10 @@ def _run_scaled_mm(c: _Call, mat2, scale_a, scale_b, scale_result, fast: bool, y
     peer_array = (ctypes.c_void_p * max(len(peers), 1))(*[ctypes.c_void_p(int(p)) for p in peers])
     with torch.cuda.device(dev):
         ws, ws_ptr, ws_bytes = _workspace(L, c.kernel, a.data_ptr(), lda, bt.data_ptr(), ldb, c.M, c.N, c.K,
-                                          c.preset.nfma, c.decision.S, dev)
+                                          c.preset.code, c.decision.S, dev)
         rc = L.mmb200_scaled_mm_peers(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb,
                                       _lib.FMT_CODES[c.fb], y.data_ptr(), ldd, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]],
-                                      c.M, c.N, c.K, c.preset.nfma, int(fast), c.decision.S,
+                                      c.M, c.N, c.K, c.preset.code, int(fast), c.decision.S,
                                       _lib.SCHEME_CODES[c.scheme], pa, pb, pr, _kernel_code(c.kernel), ws_ptr, ws_bytes,
                                       peer_array, len(peers), _stream_ptr(dev))
     _lib.check("mmb200_scaled_mm_peers", rc)
@@ -363,7 +371,7 @@ def scaled_mm_into(y, peers, input, mat2, scale_a, scale_b, scale_result=None, u
         if peers:
             raise ValueError("scaled_mm_into(): K == 0 with peer buffers is not supported")
         return y
-    c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+    c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme, bool(use_fast_accum))
     return _run_scaled_mm(c, mat2, scale_a, scale_b, scale_result, bool(use_fast_accum), y=y, peers=tuple(peers))
 
 
@@ -384,7 +392,7 @@ def scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_d
     if c.early:
         y = torch.zeros(c.M, c.N, dtype=c.od, device=input.device)
     else:
-        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme, bool(use_fast_accum))
         y = _run_scaled_mm(c, mat2, scale_a, scale_b, scale_result, bool(use_fast_accum))
     if out is None:
         return y
@@ -427,7 +435,10 @@ def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=Non
              and xs.data_ptr() % 16 == 0 and os.environ.get("MMAEMU_B200_WORKSPACE", "1") != "0")
     L = _lib.load() if fused else None
     if fused:
-        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+        c.scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme, bool(use_fast_accum))
+        if c.preset.late_c:
+            raise UnsupportedFeatureError(f"quantized_scaled_mm(): preset {c.preset.name!r} runs on the integer kernel, "
+                                          f"which has no quantisation pass; quantise with torch and call scaled_mm")
         dev = x.device
         bt = mat2.detach().t()
         ldb = bt.stride(0) if c.N > 1 else c.K
@@ -453,7 +464,7 @@ def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=Non
         rc = L.mmb200_quantize_scaled_mm_ws(xs.data_ptr(), xs.stride(0) if c.M > 1 else c.K,
                                             1 if xs.dtype == torch.float32 else 2, pq, xq.data_ptr(), c.K, bt.data_ptr(),
                                             ldb, _lib.FMT_CODES[c.fb], y.data_ptr(), c.N,
-                                            _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K, c.preset.nfma,
+                                            _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K, c.preset.code,
                                             int(bool(use_fast_accum)), c.decision.S, _lib.SCHEME_CODES[c.scheme], pa, pb,
                                             pr, ws.data_ptr(), n, _stream_ptr(dev))
     _lib.check("mmb200_quantize_scaled_mm_ws", rc)
@@ -484,7 +495,7 @@ def accumulate(a, b, *, use_fast_accum, profile=None, splitk="auto", backend="au
         raise UnsupportedFeatureError("inference only: an input requires grad while grad mode is enabled")
     prof = get_profile(profile)
     preset = get_preset(prof.preset)
-    _emit_profile_warning(prof)
+    _emit_maturity(prof, preset)
     M, K, N = a.shape[0], a.shape[1], b.shape[0]
     fast = bool(use_fast_accum)
     if M == 0 or N == 0 or K == 0:
@@ -493,16 +504,16 @@ def accumulate(a, b, *, use_fast_accum, profile=None, splitk="auto", backend="au
                               use_fast_accum=fast, profile=prof, splitk=splitk, layout_std=True)
     kernel = _kernel_choice(backend)
     _require_device(a.device)
-    scheme = check_plan(preset, K, decision.S, decision.scheme)
+    scheme = check_plan(preset, K, decision.S, decision.scheme, fast)
     dev = a.device
     au, bu = a.detach().contiguous(), b.detach().contiguous()
     acc = torch.empty((M, N), dtype=torch.float32, device=dev)
     L = _lib.load()
     with torch.cuda.device(dev):
-        ws, ws_ptr, ws_bytes = _workspace(L, kernel, au.data_ptr(), K, bu.data_ptr(), K, M, N, K, preset.nfma,
+        ws, ws_ptr, ws_bytes = _workspace(L, kernel, au.data_ptr(), K, bu.data_ptr(), K, M, N, K, preset.code,
                                           decision.S, dev)
         rc = L.mmb200_accumulate_ws(au.data_ptr(), K, _lib.FMT_CODES[fa], bu.data_ptr(), K, _lib.FMT_CODES[fb],
-                                    acc.data_ptr(), N, M, N, K, preset.nfma, int(fast), decision.S,
+                                    acc.data_ptr(), N, M, N, K, preset.code, int(fast), decision.S,
                                     _lib.SCHEME_CODES[scheme], _kernel_code(kernel), ws_ptr, ws_bytes, _stream_ptr(dev))
     _lib.check("mmb200_accumulate_ws", rc)
     del ws
@@ -519,7 +530,7 @@ def explain(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_dty
             c = _prepare(input, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out, profile,
                          splitk, backend, dry=True)
             if not (c.early or c.unchanged_out):
-                check_plan(c.preset, c.K, c.decision.S, c.decision.scheme)
+                check_plan(c.preset, c.K, c.decision.S, c.decision.scheme, bool(use_fast_accum))
         cp.warnings = list(c.notes) + [str(w.message) for w in seen]
         cp.profile, cp.preset, cp.preset_maturity = c.profile.name, c.preset.name, c.preset.maturity
         cp.split = c.decision

@@ -50,7 +50,10 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   if (M < 0 || N < 0 || K < 0) return MMB200_ERR_BAD_ARG;
   if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
   if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
-  if (nfma != 16 && nfma != 32) return MMB200_ERR_UNSUPPORTED;
+  if (nfma != MMB200_PRESET_ADA && nfma != MMB200_PRESET_HOPPER && nfma != MMB200_PRESET_B200_MMA_SYNC)
+    return MMB200_ERR_UNSUPPORTED;
+  // no GEMM level is characterised for the late-accumulator preset: unsplit fast accumulation only
+  if (nfma == MMB200_PRESET_B200_MMA_SYNC && (!fast || S != 1)) return MMB200_ERR_UNSUPPORTED;
   if (S < 1 || scheme < MMB200_SCHEME_NONE || scheme > MMB200_SCHEME_CONTIGUOUS) return MMB200_ERR_BAD_ARG;
   if (S > 1 && scheme == MMB200_SCHEME_NONE) return MMB200_ERR_BAD_ARG;
   if (S > MMB200_MAX_SPLITS) return MMB200_ERR_TOO_LARGE;

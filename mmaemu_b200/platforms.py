@@ -2,8 +2,9 @@
 
 Host-side data, restating the reference's profile registry (astding/mmaemu, mmaemu/platform/profiles.py:76-235):
 a profile pairs an instruction preset with the emulated platform's workspace size (which decides split-K), its
-split-K table and the calls its cuBLASLt rejects. The six profiles of the scaled_mm path are provided, plus
-`hopper-experimental` (hopper numerics without a platform: split-K can never be resolved automatically).
+split-K table and the calls its cuBLASLt rejects. The six profiles of the scaled_mm path are provided, plus the two
+without a platform, for which split-K can never be resolved automatically: `hopper-experimental` (hopper numerics)
+and `b200-mma-sync-experimental` (the late-accumulator preset; unsplit fast accumulation only).
 
 The emulated GPUs are an RTX 4060 and an H100 PCIe; a B200 is never one of them, so the reference's "live cuBLASLt
 query on the profile's own GPU" step does not exist here (matches_device is always False).
@@ -103,10 +104,17 @@ PROFILES = {p.name: p for p in (
             splitk_table=None, rejects=(), maturity="experimental", splitk_maturity="none",
             description="hopper numerics without a reference platform (H100 SXM, H200, other cuBLASLt versions): no "
                         "split-K table, so splitk='auto' always raises SplitKUnknownError"),
+    Profile(name="b200-mma-sync-experimental", preset="b200_mma_sync", gpu_name=None, capability=(10, 0),
+            sm_count=None, cublaslt_version=None, caller=_TORCH, torch_version=None, workspace_bytes=None, align=None,
+            splitk_table=None, rejects=(), maturity="experimental", splitk_maturity="none",
+            description="fits the toolbox B200 mma.sync (HMMA-rewrite) vectors; NOT a model of sm_120 / RTX 5070 Ti; "
+                        "NOT B200 cuBLAS; no split-K table: splitk='auto' always raises SplitKUnknownError"),
 )}
 
 
 def profile_maturity_warning(p: Profile, preset_validated: bool = True):
+    """Warning text of an experimental profile whose preset is validated (an experimental preset warns by itself),
+    else None (profiles.py:211-216)."""
     if p.maturity != "experimental" or not preset_validated:
         return None
     return f"profile {p.name!r} is experimental: {p.description}"

@@ -44,6 +44,53 @@ def test_scaled_mm_profiles(profile, fast):
     assert y.dtype == torch.bfloat16 and y.device == DEV and np.array_equal(bits(y), want)
 
 
+def test_late_accumulator_profile():
+    """profile 'b200-mma-sync-experimental' (preset b200_mma_sync, mmaemu/platform/profiles.py:202-208): the reference's
+    own outputs of the golden fixture through scaled_mm / accumulate, the maturity warning, and the reference's errors
+    for what it does not characterise (slow accumulation, split-K, an automatic split decision)."""
+    import golden_cases as G
+    from mmaemu_b200 import numerics
+    numerics._reset_warnings_for_tests()
+    prof = G.LATE_PROFILE
+    for i, c in enumerate(G.late_preset_cases()):
+        a, b = c.load()
+        ta, tb = torch.from_numpy(a).to(DEV).view(F8[c.fa]), torch.from_numpy(b).to(DEV).view(F8[c.fb])
+        with warnings.catch_warnings(record=True) as seen:
+            warnings.simplefilter("always")
+            if c.api == "accumulate":
+                y = mm.accumulate(ta, tb, use_fast_accum=True, profile=prof, splitk=1)
+            else:
+                sr = None if c.scale_result is None else torch.tensor(float(c.scale_result), device=DEV)
+                y = mm.scaled_mm(ta, tb.t(), torch.tensor(float(c.scale_a), device=DEV),
+                                 torch.tensor(float(c.scale_b), device=DEV), scale_result=sr,
+                                 out_dtype=getattr(torch, c.out), use_fast_accum=True, profile=prof, splitk=1)
+        assert np.array_equal(bits(y), c.want()), c.id
+        experimental = [w for w in seen if issubclass(w.category, mm.ExperimentalPresetWarning)]
+        assert len(experimental) == (1 if i == 0 else 0)                      # once per process and preset
+        if i == 0:
+            assert "NOT B200 cuBLAS" in str(experimental[0].message)
+    a, b, ta, tb = operands(32, 48, 256, seed=9)
+    s = torch.tensor(1.0, device=DEV)
+    with pytest.raises(mm.UnsupportedFeatureError, match="slow accumulation"):
+        mm.scaled_mm(ta, tb.t(), s, s, out_dtype=torch.bfloat16, use_fast_accum=False, profile=prof, splitk=1)
+    with pytest.raises(mm.UnsupportedFeatureError, match="split-K"):
+        mm.scaled_mm(ta, tb.t(), s, s, out_dtype=torch.bfloat16, use_fast_accum=True, profile=prof,
+                     splitk=(2, "contiguous"))
+    with pytest.raises(mm.SplitKUnknownError):
+        mm.scaled_mm(ta, tb.t(), s, s, out_dtype=torch.bfloat16, use_fast_accum=True, profile=prof)
+    with pytest.raises(mm.UnsupportedFeatureError):
+        mm.quantized_scaled_mm(torch.randn(32, 256, device=DEV), s, tb.t(), s, s, out_dtype=torch.bfloat16,
+                               use_fast_accum=True, profile=prof, splitk=1)
+    # the chain function of the backend object (what the reference's executor calls) serves the preset as well
+    from mmaemu_b200.backend import B200Backend
+
+    class Req:
+        device, fmt_a, fmt_b, preset = DEV, "e4m3", "e4m3", "b200_mma_sync"
+    got = B200Backend().chain_fn(Req())(ta.view(torch.uint8), tb.view(torch.uint8))
+    assert np.array_equal(bits(got), oracle.accumulate(a, b, preset=288, fast=True))
+    assert "integer kernel only" in B200Backend("fast").supports(Req())
+
+
 def test_config1_ada_256_cube():
     """M = N = K = 256, profile 'ada', seeds 0 / 1, scales 0.5 and 1.25, bf16 out, split-K from the table."""
     A = (torch.randn(256, 256, generator=torch.Generator().manual_seed(0)) * 2).to(torch.float8_e4m3fn)

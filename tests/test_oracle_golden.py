@@ -18,6 +18,11 @@ def test_reference_outputs(case):
     _check(case)
 
 
+@pytest.mark.parametrize("case", G.late_preset_cases(), ids=lambda c: c.id)
+def test_reference_outputs_of_the_late_accumulator_preset(case):
+    _check(case)
+
+
 @pytest.mark.parametrize("case", G.epilogue_tie_cases(), ids=lambda c: c.id)
 def test_rtx4060_double_rounding_ties(case):
     _check(case)
@@ -39,5 +44,8 @@ def test_fixture_coverage():
     assert {(c.fa, c.fb) for c in ref} == {("e4m3", "e4m3"), ("e5m2", "e4m3"), ("e4m3", "e5m2")}
     assert {c.scheme for c in ref} == {"none", "serial", "pairwise", "contiguous"}
     assert {c.fast for c in ref} == {True, False} and {c.api for c in ref} == {"scaled_mm", "accumulate"}
+    late = G.late_preset_cases()
+    assert len(late) == 13 and {c.nfma for c in late} == {288} and all(c.fast and c.S == 1 for c in late)
+    assert {(c.fa, c.fb) for c in late} == {("e4m3", "e4m3"), ("e5m2", "e4m3"), ("e4m3", "e5m2")}
     assert len(G.epilogue_tie_cases()) == 64 and len(G.h100_cases()) == 122 and len(G.h100_rejected()) == 2
     assert {c.S for c in G.h100_cases()} == {1, 2, 3, 4, 5, 6}

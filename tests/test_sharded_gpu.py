@@ -2,7 +2,8 @@
 plumbing. Both ways of assembling the result are run -- the kernel's epilogue storing into every GPU's copy through
 peer pointers ("peer"), and row slabs followed by an all-gather ("nccl") -- and every rank's assembled result must
 equal the single-GPU result of the whole call and, on sampled rows of every rank's slab, the oracle. Ragged row counts
-(a last slab that is shorter, a rank without rows) and split-K plans (decided on the whole shape) are covered.
+(a last slab that is shorter, a rank without rows), column groups (grid 1 x 2, with a rank without columns) and
+split-K plans (decided on the whole shape) are covered.
 NVLS is switched off for NCCL: these child processes come and go."""
 import os
 import socket
@@ -70,6 +71,15 @@ def _worker(rank, port, q):
                         it = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[y.element_size()]
                         same = y.shape == (M, N) and bool(torch.equal(y.view(it), whole.view(it)))
                         results.append((i, mode, local, same))
+                    # column groups (grid 1 x 2): whole operands, then only this rank's columns of mat2
+                    n0, n1 = shard_rows(N, WORLD, rank)
+                    for local2 in (False, True):
+                        extra = dict(mat2_is_local=True, full_cols=N) if local2 else {}
+                        y = sharded_scaled_mm(ad, bd[n0:n1].t() if local2 else bd.t(), sa, sb, assemble=mode,
+                                              grid=(1, WORLD), **kw, **extra)
+                        torch.cuda.synchronize(dev)
+                        same = y.shape == (M, N) and bool(torch.equal(y.view(it), whole.view(it)))
+                        results.append((i, mode, "columns" + ("-local" if local2 else ""), same))
                     # twice in a row with the same shape: the symmetric buffer is reused, the first result stays intact
                     y1 = sharded_scaled_mm(ad, bd.t(), sa, sb, assemble=mode, **kw)
                     y2 = sharded_scaled_mm(ad, bd.t(), sb, sa, assemble=mode, **kw)
@@ -104,4 +114,4 @@ def test_two_gpus_assemble_the_whole_result():
         rank, results = q.get(timeout=10)
         bad = [r for r in results if not r[3]]
         assert not bad, f"rank {rank}: {bad}"
-        assert len(results) == len(CASES) * 7
+        assert len(results) == len(CASES) * 11

@@ -1,5 +1,5 @@
-"""The multi-GPU sharding logic on two CPU ranks (gloo): row partition, split-K decided on the full shape, all-gather
-of equal and ragged slabs. The per-rank compute is a stand-in that calls the CPU oracle, so the assembled result must
+"""The multi-GPU sharding logic on two and four CPU ranks (gloo): row slabs and row x column grids, split-K decided
+on the full shape, all-gather of equal and ragged rectangles. The per-rank compute is a stand-in that calls the CPU oracle, so the assembled result must
 equal the oracle on the whole problem bit for bit."""
 import os
 import socket
@@ -10,7 +10,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from mmaemu_b200.sharding import shard_rows
+from mmaemu_b200.sharding import shard_grid, shard_rows
 
 F8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
 
@@ -26,10 +26,21 @@ def test_shard_rows_cover_every_row_once():
         shard_rows(10, 2, 2)
 
 
-def _worker(rank, world, port, M, N, K, profile, out_name, local, q):
+def test_shard_grid():
+    assert shard_grid(16384, 16384, 8) == (8, 1) and shard_grid(16, 8192, 8) == (8, 1)      # default: row slabs
+    assert shard_grid(16384, 16384, 8, "auto") == (8, 1)                                    # ties keep the row slabs
+    assert shard_grid(16, 8192, 8, "auto") == (1, 8)                                        # nothing to cut along M
+    assert shard_grid(256, 8192, 8, "auto") == (2, 4)
+    assert shard_grid(100, 100, 4, (2, 2)) == (2, 2)
+    for bad in ((2, 3), (0, 4), "rows", 4):
+        with pytest.raises(ValueError):
+            shard_grid(100, 100, 4, bad)
+
+
+def _worker(rank, world, port, M, N, K, profile, out_name, local, q, grid=None, local2=False, splitk="auto"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
-    from mmaemu_b200.sharding import shard_rows, sharded_scaled_mm
+    from mmaemu_b200.sharding import shard_grid, shard_rows, sharded_scaled_mm
     from oracle import oracle
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -40,19 +51,23 @@ def _worker(rank, world, port, M, N, K, profile, out_name, local, q):
         seen = []
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
-            m0, m1 = shard_rows(M, world, rank)
+            gm, gn = shard_grid(M, N, world, grid)
+            m0, m1 = shard_rows(M, gm, rank // gn)
+            n0, n1 = shard_rows(N, gn, rank % gn) if gn > 1 else (0, N)
             extra = dict(input_is_local=True, full_rows=M) if local else {}      # only this rank's rows are passed
-            y = sharded_scaled_mm(a[m0:m1] if local else a, bt.t(), torch.tensor(0.25), torch.tensor(3.0),
-                                  out_dtype=od, use_fast_accum=True, profile=profile, compute=_oracle_compute(seen),
-                                  **extra)
+            if local2:                                                           # ... and only its columns of mat2
+                extra.update(mat2_is_local=True, full_cols=N)
+            y = sharded_scaled_mm(a[m0:m1] if local else a, bt[n0:n1].t() if local2 else bt.t(), torch.tensor(0.25),
+                                  torch.tensor(3.0), out_dtype=od, use_fast_accum=True, profile=profile,
+                                  compute=_oracle_compute(seen), grid=grid, splitk=splitk, **extra)
             from mmaemu_b200.splitk import resolve_splitk
             d = resolve_splitk(M, N, K, a_dtype=a.dtype, b_dtype=bt.dtype, out_dtype=od, use_fast_accum=True,
-                               profile=profile)
+                               profile=profile, splitk=splitk)
         want = oracle.scaled_mm(a.view(torch.uint8).numpy(), bt.view(torch.uint8).numpy(), 0.25, 3.0, out=out_name,
                                 fmt_a="e5m2", fmt_b="e4m3", preset=profile, fast=True, S=d.S, scheme=d.scheme)
         it = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[y.element_size()]
         got = y.contiguous().view(it).numpy().view(want.dtype)
-        called = [] if m1 == m0 else [1 if d.S == 1 else (d.S, d.scheme)]     # a rank without rows computes nothing
+        called = [] if (m1 == m0 or n1 == n0) else [1 if d.S == 1 else (d.S, d.scheme)]   # no rectangle: no compute
         ok = y.shape == (M, N) and np.array_equal(got, want) and seen == called
         q.put((rank, bool(ok), d.S))
         dist.barrier()
@@ -100,6 +115,28 @@ def test_two_ranks_assemble_the_oracle_result(M, N, K, profile, out, local):
         assert p.exitcode == 0
     results = sorted(q.get(timeout=5) for _ in range(2))
     assert [r[1] for r in results] == [True, True], results
+
+
+@pytest.mark.parametrize("world,grid,M,N,K,profile,out,local,local2,splitk", [
+    (2, (1, 2), 256, 64, 8192, "hopper", "bfloat16", False, False, "auto"),        # columns only; S from the H100 table
+    (4, (2, 2), 200, 320, 1024, "ada", "float16", False, False, (3, "pairwise")),  # ragged both ways (128 + 72, 256 + 64)
+    (4, (2, 2), 200, 320, 1024, "hopper", "float8_e4m3fn", True, True, 1),         # only own rows and columns are passed
+    (4, "auto", 16, 1024, 512, "hopper", "float32", False, True, (2, "contiguous")),   # a decode shape: auto = (1, 4)
+    (4, (1, 4), 128, 304, 256, "ada", "bfloat16", False, False, 1),                # the last rank owns no columns
+])
+def test_a_grid_of_ranks_assembles_the_oracle_result(world, grid, M, N, K, profile, out, local, local2, splitk):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, profile, out, local, q, grid, local2, splitk))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    results = sorted(q.get(timeout=5) for _ in range(world))
+    assert [r[1] for r in results] == [True] * world, results
 
 
 def _worker_reject(rank, world, port, case, q):
