@@ -5,7 +5,7 @@
  * caller; nothing is allocated internally unless a function says so. All launches are asynchronous on the given
  * cudaStream_t (passed as void*; NULL = the legacy default stream). Functions return MMB200_OK (0) or a negative
  * status, never throw and never abort. Mutable state of the library: per-device function attributes that are set once;
- * the per-device memory pool of mmb200_scaled_mm_host; the fixed scratch array of mmb200_scaled_mm_static with its
+ * the per-device memory pool, internal streams and events of mmb200_scaled_mm_host; the fixed scratch array of mmb200_scaled_mm_static with its
  * cached per-device address; the launch counter; the process-wide test hooks of mmb200_test_hooks.
  *
  * Operands are FP8 code bytes: A is [M, K] row-major with leading dimension lda (bytes), B is [N, K] row-major with
@@ -109,7 +109,15 @@ int mmb200_scaled_mm(const void *A_dev, int64_t lda, int fmt_a, const void *B_de
 /* Same computation for HOST operands and a HOST result: copies A and B to the current device, runs the kernel, copies
  * D back and waits for it. Device staging memory, including the scratch memory of the staged kernels, comes from a
  * stream-ordered memory pool of the library (cudaMallocFromPoolAsync; the pool keeps freed memory for the next call) and
- * is returned to it before the call returns. Host buffers should be pinned for full copy speed but need not be. */
+ * is returned to it before the call returns. Host buffers should be pinned for full copy speed but need not be.
+ * Calls that move 8 MiB or more and have at least two slabs of about 128 output tiles are pipelined: B is copied and
+ * decoded once, the rows of A are cut into at most 8 slabs (multiples of 128 rows), each on an internal stream of its
+ * own (copy of its rows, its kernels, copy-back of its outputs), so that the copies of some slabs overlap the kernels
+ * of others; the caller's stream waits for all of it. Rows are independent of one another
+ * and the plan is that of the whole call, so the result is the same bits. One pipelined call at a time per device
+ * (others wait on a mutex); MMAEMU_B200_HOST_PIPELINE=0 in the environment turns the slabs off. When a bounded wait
+ * inside a kernel runs out the call returns MMB200_ERR_TIMEOUT; D is then not written by an unpipelined call and
+ * unspecified after a pipelined one (finished slabs have been copied back). */
 int mmb200_scaled_mm_host(const void *A_host, int64_t lda, int fmt_a, const void *B_host, int64_t ldb, int fmt_b,
                           void *D_host, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
                           int scheme, float scale_a, float scale_b, const float *scale_result /* host, nullable */,

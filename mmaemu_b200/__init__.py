@@ -28,6 +28,7 @@ _LAZY = {
     "B200Backend": ("mmaemu_b200.backend", "B200Backend"), "BACKEND": ("mmaemu_b200.backend", "BACKEND"),
     "sharded_scaled_mm": ("mmaemu_b200.sharding", "sharded_scaled_mm"),
     "scaled_mm_into": ("mmaemu_b200.api", "scaled_mm_into"),
+    "scaled_mm_host": ("mmaemu_b200.api", "scaled_mm_host"),
 }
 
 __all__ = ["__version__", *sorted(_LAZY), "MmaemuError", "ReferenceRejectsError", "UnsupportedFeatureError",

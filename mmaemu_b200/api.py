@@ -405,6 +405,62 @@ def scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_d
     return out
 
 
+def scaled_mm_host(input, mat2, scale_a, scale_b, scale_result=None, out_dtype=None, use_fast_accum=False, *, out=None,
+                   profile=None, splitk="auto", backend="auto", device=None):
+    """scaled_mm for operands that live in HOST memory: CPU tensors in, a CPU tensor out, computed on `device` (default:
+    the current CUDA device) by the library's host-buffer entry point (mmb200_scaled_mm_host), which stages the operands
+    on the device, overlaps the copies with the kernels slab by slab for large calls, and waits for the result.
+
+    Arguments, checks, exceptions and their order are those of scaled_mm (the call is validated from the tensors'
+    metadata). input [M, K] and mat2 [K, N] (column-major) are FP8 CPU tensors, pinned for full copy speed; the scales
+    are one-element fp32 tensors. out: optional row-major [M, N] CPU tensor of the output dtype to write into (a new
+    pinned tensor otherwise). The result equals scaled_mm on the same operands bit for bit."""
+    from .sharding import validate_full_call
+    for name, t in (("input", input), ("mat2", mat2)):
+        if isinstance(t, torch.Tensor) and t.device.type != "cpu":
+            raise ValueError(f"scaled_mm_host(): {name} is on {t.device}; this entry point takes host tensors "
+                             f"(use scaled_mm for device tensors)")
+    c = validate_full_call(input, mat2, scale_a, scale_b, None, scale_result, out_dtype, use_fast_accum, profile, splitk,
+                           backend)
+    if out is not None:
+        if not isinstance(out, torch.Tensor) or out.device.type != "cpu" or out.dtype != c.od or \
+                tuple(out.shape) != (c.M, c.N) or (c.N > 1 and out.stride(1) != 1) or (c.M > 1 and out.stride(0) < c.N):
+            raise ValueError(f"scaled_mm_host(): out must be a row-major CPU tensor of shape {(c.M, c.N)} and dtype {c.od}")
+    if c.early:
+        y = out if out is not None else torch.empty((c.M, c.N), dtype=c.od)
+        return y.zero_()
+    fast = bool(use_fast_accum)
+    scheme = check_plan(c.preset, c.K, c.decision.S, c.decision.scheme, fast)
+    _emit_maturity(c.profile, c.preset)
+    if not torch.cuda.is_available():
+        raise BackendUnavailableError("mmaemu_b200 runs on sm_100 CUDA devices only and has no CPU fallback; no CUDA "
+                                      "device is available to scaled_mm_host()")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    _require_device(dev)
+    a = input.detach()
+    bt = mat2.detach().t()                               # [N, K] with unit stride along K
+    if a.stride(1) != 1 and c.K > 1:
+        a = a.contiguous()
+    lda = a.stride(0) if c.M > 1 else c.K
+    ldb = bt.stride(0) if c.N > 1 else c.K
+    y = out if out is not None else torch.empty((c.M, c.N), dtype=c.od, pin_memory=True)
+    ldd = y.stride(0) if c.M > 1 else c.N
+    sr = None if scale_result is None else ctypes.c_float(float(scale_result.detach().reshape(()).item()))
+    L = _lib.load()
+    with torch.cuda.device(dev):
+        rc = L.mmb200_scaled_mm_host(a.data_ptr(), lda, _lib.FMT_CODES[c.fa], bt.data_ptr(), ldb, _lib.FMT_CODES[c.fb],
+                                     y.data_ptr(), ldd, _lib.OUT_CODES[OUT_DTYPE_NAMES[c.od]], c.M, c.N, c.K,
+                                     c.preset.code, int(fast), c.decision.S, _lib.SCHEME_CODES[scheme],
+                                     ctypes.c_float(float(scale_a.detach().reshape(()).item())),
+                                     ctypes.c_float(float(scale_b.detach().reshape(()).item())),
+                                     None if sr is None else ctypes.cast(ctypes.pointer(sr), ctypes.c_void_p),
+                                     _kernel_code(c.kernel), _stream_ptr(dev))
+    _lib.check("mmb200_scaled_mm_host", rc)
+    return y
+
+
 def quantized_scaled_mm(x, quant_scale, mat2, scale_a, scale_b, scale_result=None, out_dtype=None,
                         use_fast_accum=False, *, profile=None, splitk="auto", return_codes=False):
     """scaled_mm on activations that are still in fp32 or bf16: the quantisation to E4M3,

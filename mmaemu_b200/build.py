@@ -49,13 +49,21 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     env.pop("CXX", None)
     OBJ.mkdir(exist_ok=True)
     nvcc = nvcc_path()
+    # a unit is compiled again when its object is older than its source, a shared header or this file
+    shared = [*CSRC.glob("*.cuh"), PKG.parent / "include" / "mmaemu_b200.h", Path(__file__)]
+    newest_shared = max(d.stat().st_mtime for d in shared)
     jobs = []
     for i, (src, defines) in enumerate(UNITS):
         obj = OBJ / f"{Path(src).stem}_{i}.o"
         cmd = [nvcc, *NVCC_FLAGS, *defines, *(["-Xptxas", "-v"] if verbose else []), "-c", str(CSRC / src), "-o", str(obj)]
-        jobs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)))
+        fresh = (not force and not verbose and obj.exists()
+                 and obj.stat().st_mtime > max(newest_shared, (CSRC / src).stat().st_mtime))
+        proc = None if fresh else subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+        jobs.append((cmd, obj, proc))
     failed = None
     for cmd, obj, proc in jobs:
+        if proc is None:
+            continue
         out, _ = proc.communicate()
         if verbose or proc.returncode:
             sys.stderr.write(out)

@@ -2,6 +2,7 @@
 // mmb200_scaled_mm_host, which stages host operands through the stream-ordered allocator.
 #include <atomic>
 #include <mutex>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -43,7 +44,8 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
         int out_dtype, int M, int N, int K, int nfma, int fast, int S, int scheme, const float* sa, const float* sb,
         const float* sr, int epilogue, int patch, int kernel, void* stream, void* workspace = nullptr,
         size_t workspace_bytes = 0, const void* a_hp = nullptr, int64_t ld_hp = 0, int hp_dtype = 0,
-        const float* quant_scale = nullptr, void* const* peer_D = nullptr, int n_peers = 0) {
+        const float* quant_scale = nullptr, void* const* peer_D = nullptr, int n_peers = 0,
+        unsigned char* shared_b = nullptr) {
   if (n_peers < 0 || n_peers > MMB200_MAX_PEERS || (n_peers > 0 && !peer_D)) return MMB200_ERR_BAD_ARG;
   for (int q = 0; q < n_peers; ++q)
     if (!peer_D[q]) return MMB200_ERR_BAD_ARG;
@@ -87,6 +89,7 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   p.patch_nonfinite = patch;
   p.n_peers = n_peers;
   for (int q = 0; q < n_peers; ++q) p.peer_D[q] = peer_D[q];
+  p.shared_b = shared_b;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t err;
@@ -103,8 +106,9 @@ int run(const void* A, int64_t lda, int fmt_a, const void* B, int64_t ldb, int f
   // fast kernels: every plan with enough scratch memory (staged), unsplit plans without; else the integer kernel
   const bool direct_ok = mmb::fast_supports(p, nfma);
   const bool staged_ok = mmb::staged_supports(p, nfma) && workspace &&
-                         workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S, false) &&
+                         workspace_bytes >= mmb::staged_workspace_bytes(M, N, K, S, false, shared_b != nullptr) &&
                          !(reinterpret_cast<uintptr_t>(workspace) & 127);
+  if (shared_b && !staged_ok) return MMB200_ERR_UNSUPPORTED;      // only the staged kernels read a shared B area
   if (kernel == MMB200_KERNEL_FAST && !direct_ok && !staged_ok) return MMB200_ERR_UNSUPPORTED;
   if (a_hp && (!staged_ok || kernel == MMB200_KERNEL_INTEGER)) return MMB200_ERR_UNSUPPORTED;   // only the pre-decode pass quantises
   if (kernel != MMB200_KERNEL_INTEGER && staged_ok) {
@@ -144,6 +148,52 @@ cudaError_t staging_pool(cudaMemPool_t* pool) {
     if (err != cudaSuccess) return err;
   }
   *pool = pools[dev];
+  return cudaSuccess;
+}
+
+// Internal streams and events of the host-buffer entry point (one set per device, created on first use; a call holds
+// the mutex while it uses them).
+struct HostPipeline {
+  static constexpr int STREAMS = 8;                     // one per slab: no slab waits behind another one
+  std::mutex mu;
+  cudaStream_t s[STREAMS] = {};
+  cudaEvent_t start = nullptr, b_ready = nullptr, done[STREAMS] = {};
+  bool ready = false;
+};
+constexpr size_t PIPELINE_MIN_BYTES = (size_t)8 << 20;   // operands + output below this: one slab, the caller's stream
+constexpr int PIPELINE_SLAB_TILES = 128;                // output tiles of 128 x 128 per slab: at least this many (a slab of
+                                                        // at most one wave of CTAs lets the next slab's CTAs fill its tail)
+constexpr int PIPELINE_MAX_SLABS = HostPipeline::STREAMS;
+
+// MMAEMU_B200_HOST_PIPELINE: "0" = copy, compute, copy back on one stream; a number from 2 to 8 = that many slabs
+// whatever the size of the call (tests and tuning); anything else = the automatic choice. Returns 0, the number, or -1.
+int host_pipeline_setting() {
+  const char* env = std::getenv("MMAEMU_B200_HOST_PIPELINE");
+  if (!env || !env[0]) return -1;
+  const int v = std::atoi(env);
+  if (v == 0 && env[0] == '0') return 0;
+  return (v >= 2 && v <= PIPELINE_MAX_SLABS) ? v : -1;
+}
+
+cudaError_t host_pipeline(HostPipeline** out) {
+  static std::mutex mu;
+  static HostPipeline pipes[64];
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  HostPipeline& hp = pipes[dev];
+  if (!hp.ready) {
+    for (int q = 0; q < HostPipeline::STREAMS; ++q) {
+      if (!hp.s[q] && (err = cudaStreamCreateWithFlags(&hp.s[q], cudaStreamNonBlocking)) != cudaSuccess) return err;
+      if (!hp.done[q] && (err = cudaEventCreateWithFlags(&hp.done[q], cudaEventDisableTiming)) != cudaSuccess) return err;
+    }
+    if (!hp.start && (err = cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming)) != cudaSuccess) return err;
+    if (!hp.b_ready && (err = cudaEventCreateWithFlags(&hp.b_ready, cudaEventDisableTiming)) != cudaSuccess) return err;
+    hp.ready = true;
+  }
+  *out = &hp;
   return cudaSuccess;
 }
 
@@ -301,48 +351,142 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
   if (out_dtype < MMB200_OUT_F32 || out_dtype > MMB200_OUT_E5M2) return MMB200_ERR_BAD_ARG;
   if (M == 0 || N == 0) return MMB200_OK;
   if (!D || ldd < N || (K > 0 && (!A || !B || lda < K || ldb < K))) return MMB200_ERR_BAD_ARG;
+  if (!fmt_ok(fmt_a) || !fmt_ok(fmt_b)) return MMB200_ERR_BAD_ARG;
+  {
+    const int rc_dev = current_device_ok();
+    if (rc_dev != MMB200_OK) return rc_dev;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t es = out_size(out_dtype);
   const size_t kpad = ((size_t)K + 15) / 16 * 16;       // dense device copies with a 16-byte aligned row stride
   const size_t a_bytes = (size_t)M * kpad, b_bytes = (size_t)N * kpad, d_bytes = (size_t)M * N * es;
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  const bool staged = K > 0 && K % 16 == 0 && S >= 1 && S <= MMB200_MAX_SPLITS && kernel != MMB200_KERNEL_INTEGER &&
+                      (nfma == MMB200_PRESET_ADA || nfma == MMB200_PRESET_HOPPER);
+  // Row slabs: with enough work the rows of A are cut into slabs, each on an internal stream of its own (copy of its
+  // rows, its kernels, copy-back of its outputs), so that the copies of some slabs overlap the kernels of others and the
+  // GPU always has a slab whose rows have arrived (rows are independent of one another; B is copied and decoded once,
+  // into a shared area). A slab on a stream of its own never waits behind another slab: with fewer streams than slabs
+  // the slab queued behind the one the GPU happened to run last ran alone at the end.
+  HostPipeline* pipe = nullptr;
+  int slab_rows = M, n_slabs = 1;
+  const int setting = host_pipeline_setting();
+  if (staged && setting != 0 && (setting > 0 || a_bytes + b_bytes + d_bytes >= PIPELINE_MIN_BYTES)) {
+    const int tiles_n = (N + 127) / 128, tiles_m = (M + 127) / 128;
+    int tile_rows = (PIPELINE_SLAB_TILES + tiles_n - 1) / tiles_n;
+    if (setting > 0) tile_rows = (tiles_m + setting - 1) / setting;
+    int slabs = (tiles_m + tile_rows - 1) / tile_rows;
+    if (slabs > PIPELINE_MAX_SLABS) {
+      tile_rows = ((M + 127) / 128 + PIPELINE_MAX_SLABS - 1) / PIPELINE_MAX_SLABS;
+      slabs = ((M + 127) / 128 + tile_rows - 1) / tile_rows;
+    }
+    if (slabs >= 2) {
+      cudaError_t perr = host_pipeline(&pipe);
+      if (perr != cudaSuccess) return cuda_fail(perr);
+      slab_rows = tile_rows * 128;
+      n_slabs = slabs;
+    }
+  }
+  // device staging: A, B, D, the three scales, then scratch memory of the staged kernels (one per slab, B shared)
+  const size_t a_off = 0, b_off = up(a_bytes), d_off = b_off + up(b_bytes), s_off = d_off + up(d_bytes);
+  const size_t sb_off = s_off + 256;
+  const size_t sb_bytes = pipe ? up(mmb::staged_shared_b_bytes(N, K)) : 0;
+  const size_t w_off = sb_off + sb_bytes;
+  const size_t w_each = staged ? up(mmb::staged_workspace_bytes(slab_rows, N, K, S, true, pipe != nullptr)) : 0;
+  const size_t total = w_off + w_each * (size_t)n_slabs;
   uint8_t* buf = nullptr;
-  const size_t a_off = 0, b_off = (a_bytes + 255) / 256 * 256, d_off = b_off + (b_bytes + 255) / 256 * 256;
-  const size_t s_off = d_off + (d_bytes + 255) / 256 * 256, w_off = s_off + 256;
-  // scratch memory for the staged kernels, when the request can use them
-  const size_t w_bytes = (K > 0 && K % 16 == 0 && S >= 1 && S <= MMB200_MAX_SPLITS && kernel != MMB200_KERNEL_INTEGER)
-                             ? mmb::staged_workspace_bytes(M, N, K, S, true) : 0;
-  const size_t total = w_off + w_bytes;
   cudaMemPool_t pool = nullptr;
   cudaError_t err = staging_pool(&pool);
   if (err != cudaSuccess) return cuda_fail(err);
+  std::unique_lock<std::mutex> lock;
+  if (pipe) lock = std::unique_lock<std::mutex>(pipe->mu);   // the internal streams and events serve one call at a time
   err = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&buf), total, pool, st);
   if (err != cudaSuccess) return cuda_fail(err);
   int rc = MMB200_OK;
   float scales[3] = {scale_a, scale_b, scale_result ? *scale_result : 1.0f};
+  int words[PIPELINE_MAX_SLABS] = {};
+  const float* sdev = reinterpret_cast<const float*>(buf + s_off);
   do {
-    if (K > 0) {
-      if (kpad != (size_t)K) {
-        err = cudaMemsetAsync(buf, 0, b_off + b_bytes, st);
+    if (K > 0 && kpad != (size_t)K) {
+      err = cudaMemsetAsync(buf, 0, b_off + b_bytes, st);
+      if (err != cudaSuccess) break;
+    }
+    if (!pipe) {
+      if (K > 0) {
+        err = cudaMemcpy2DAsync(buf + a_off, kpad, A, (size_t)lda, (size_t)K, (size_t)M, cudaMemcpyHostToDevice, st);
+        if (err != cudaSuccess) break;
+        err = cudaMemcpy2DAsync(buf + b_off, kpad, B, (size_t)ldb, (size_t)K, (size_t)N, cudaMemcpyHostToDevice, st);
         if (err != cudaSuccess) break;
       }
-      err = cudaMemcpy2DAsync(buf + a_off, kpad, A, (size_t)lda, (size_t)K, (size_t)M, cudaMemcpyHostToDevice, st);
+      err = cudaMemcpyAsync(buf + s_off, scales, sizeof(scales), cudaMemcpyHostToDevice, st);
       if (err != cudaSuccess) break;
-      err = cudaMemcpy2DAsync(buf + b_off, kpad, B, (size_t)ldb, (size_t)K, (size_t)N, cudaMemcpyHostToDevice, st);
-      if (err != cudaSuccess) break;
-    }
-    err = cudaMemcpyAsync(buf + s_off, scales, sizeof(scales), cudaMemcpyHostToDevice, st);
-    if (err != cudaSuccess) break;
-    const float* sdev = reinterpret_cast<const float*>(buf + s_off);
-    rc = mmb200_scaled_mm_ws(buf + a_off, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, buf + d_off, N,
-                             out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1,
-                             scale_result ? sdev + 2 : nullptr, kernel, w_bytes ? buf + w_off : nullptr, w_bytes, stream);
-    if (rc != MMB200_OK) break;
-    if (w_bytes) {                        // the staged kernels report a wait that ran out; D is then not copied back
-      rc = read_status(buf + w_off, M, N, K, S, st);
+      rc = mmb200_scaled_mm_ws(buf + a_off, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, buf + d_off, N,
+                               out_dtype, M, N, K, nfma, fast, S, scheme, sdev, sdev + 1,
+                               scale_result ? sdev + 2 : nullptr, kernel, w_each ? buf + w_off : nullptr, w_each, stream);
       if (rc != MMB200_OK) break;
+      if (w_each) {                       // the staged kernels report a wait that ran out; D is then not copied back
+        rc = read_status(buf + w_off, M, N, K, S, st);
+        if (rc != MMB200_OK) break;
+      }
+      err = cudaMemcpy2DAsync(D, (size_t)ldd * es, buf + d_off, (size_t)N * es, (size_t)N * es, (size_t)M,
+                              cudaMemcpyDeviceToHost, st);
+      break;
     }
-    err = cudaMemcpy2DAsync(D, (size_t)ldd * es, buf + d_off, (size_t)N * es, (size_t)N * es, (size_t)M,
-                            cudaMemcpyDeviceToHost, st);
+    // ---- row slabs on the internal streams
+    err = cudaEventRecord(pipe->start, st);                 // the allocation and earlier work of the caller's stream
+    if (err != cudaSuccess) break;
+    for (int q = 0; q < HostPipeline::STREAMS && err == cudaSuccess; ++q) err = cudaStreamWaitEvent(pipe->s[q], pipe->start, 0);
+    if (err != cudaSuccess) break;
+    cudaStream_t s0 = pipe->s[0];
+    err = cudaMemcpy2DAsync(buf + b_off, kpad, B, (size_t)ldb, (size_t)K, (size_t)N, cudaMemcpyHostToDevice, s0);
+    if (err != cudaSuccess) break;
+    err = cudaMemcpyAsync(buf + s_off, scales, sizeof(scales), cudaMemcpyHostToDevice, s0);
+    if (err != cudaSuccess) break;
+    {
+      mmb::Params pb;
+      std::memset(&pb, 0, sizeof(pb));
+      pb.B = buf + b_off; pb.ldb = (long long)kpad; pb.N = N; pb.K = K; pb.fmt_a = fmt_a; pb.fmt_b = fmt_b;
+      pb.shared_b = buf + sb_off;
+      int launches = 0;
+      err = mmb::launch_predecode_b(pb, nfma, s0, &launches);
+      if (err != cudaSuccess) break;
+      g_launches.fetch_add(launches, std::memory_order_relaxed);
+    }
+    err = cudaEventRecord(pipe->b_ready, s0);
+    if (err != cudaSuccess) break;
+    for (int i = 0; i < n_slabs && rc == MMB200_OK; ++i) {
+      cudaStream_t sq = pipe->s[i];
+      const int m0 = i * slab_rows, rows = (M - m0 < slab_rows) ? M - m0 : slab_rows;
+      uint8_t* a_dev = buf + a_off + (size_t)m0 * kpad;
+      uint8_t* d_dev = buf + d_off + (size_t)m0 * N * es;
+      uint8_t* ws = buf + w_off + (size_t)i * w_each;
+      err = cudaMemcpy2DAsync(a_dev, kpad, static_cast<const uint8_t*>(A) + (size_t)m0 * (size_t)lda, (size_t)lda,
+                              (size_t)K, (size_t)rows, cudaMemcpyHostToDevice, sq);
+      if (err != cudaSuccess) break;
+      err = cudaStreamWaitEvent(sq, pipe->b_ready, 0);
+      if (err != cudaSuccess) break;
+      rc = run(a_dev, (int64_t)kpad, fmt_a, buf + b_off, (int64_t)kpad, fmt_b, d_dev, N, out_dtype, rows, N, K, nfma,
+               fast, S, scheme, sdev, sdev + 1, scale_result ? sdev + 2 : nullptr, 1, 1, kernel, sq, ws, w_each, nullptr,
+               0, 0, nullptr, nullptr, 0, buf + sb_off);
+      if (rc != MMB200_OK) break;
+      err = cudaMemcpy2DAsync(static_cast<uint8_t*>(D) + (size_t)m0 * (size_t)ldd * es, (size_t)ldd * es, d_dev,
+                              (size_t)N * es, (size_t)N * es, (size_t)rows, cudaMemcpyDeviceToHost, sq);
+      if (err != cudaSuccess) break;
+    }
+    // back to the caller's stream: it continues when every internal stream is done (also after an error above, so
+    // that the staging memory is not freed under work that was already enqueued)
+    for (int q = 0; q < HostPipeline::STREAMS; ++q) {
+      cudaError_t e2 = cudaEventRecord(pipe->done[q], pipe->s[q]);
+      if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, pipe->done[q], 0);
+      if (e2 != cudaSuccess && err == cudaSuccess) err = e2;
+    }
+    if (err != cudaSuccess || rc != MMB200_OK) break;
+    for (int i = 0; i < n_slabs; ++i) {                      // status words of the slabs' bounded waits
+      const int m0 = i * slab_rows, rows = (M - m0 < slab_rows) ? M - m0 : slab_rows;
+      err = cudaMemcpyAsync(&words[i], buf + w_off + (size_t)i * w_each + mmb::staged_status_offset(rows, N, K, S, true),
+                            sizeof(int), cudaMemcpyDeviceToHost, st);
+      if (err != cudaSuccess) break;
+    }
   } while (0);
   cudaError_t ferr = cudaFreeAsync(buf, st);
   cudaError_t serr = cudaStreamSynchronize(st);   // the scales array and the caller's buffers must outlive the copies
@@ -350,6 +494,8 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
   if (err != cudaSuccess) return cuda_fail(err);
   if (ferr != cudaSuccess) return cuda_fail(ferr);
   if (serr != cudaSuccess) return cuda_fail(serr);
+  for (int i = 0; i < n_slabs; ++i)
+    if (words[i] != 0) return MMB200_ERR_TIMEOUT;   // slabs are copied back as they finish: D is unspecified then
   return MMB200_OK;
 }
 

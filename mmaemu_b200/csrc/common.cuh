@@ -42,6 +42,11 @@ struct Params {
   int* ws_flag_b;
   int* status;
   int k_tiles;
+  // B decoded by an earlier launch (the host-buffer entry point decodes B once and runs the rows of A slab by slab):
+  // shared_b holds B's tile images followed by its column flags (staged_shared_b_bytes); the launch then neither
+  // decodes B nor clears its flags. only_b: decode B into shared_b and launch nothing else.
+  unsigned char* shared_b;
+  int only_b;
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
   // multi-GPU assembly: the same output element is also stored at the same index of every peer_D[i] (device pointers
   // into other GPUs' memory, mapped into this process), so that every GPU ends up with the whole result
@@ -273,12 +278,16 @@ bool fast_supports(const Params& p, int nfma);
 // Staged fast kernel: scratch bytes it needs for a shape, and the launch (pre-decode of both operands, then the GEMM).
 // `launches` is increased by the number of kernels launched.
 bool staged_supports(const Params& p, int nfma);            // like fast_supports, any plan
-size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices);
+size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices, bool shared_b = false);
+// Bytes of a shared B area (tile images of every 128-column group, then one int per column), and the launch that fills
+// it (p.B, p.ldb, p.N, p.K, the formats; p.shared_b = the area, 128-byte aligned).
+size_t staged_shared_b_bytes(int N, int K);
+cudaError_t launch_predecode_b(const Params& p, int nfma, cudaStream_t stream, int* launches);
 cudaError_t launch_staged(const Params& p, int nfma, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                           int* launches);
 // Byte offset, inside the scratch memory of a staged launch, of the int32 status word (0, or 1 when a bounded wait ran
 // out and the output was not written); the same with and without K slices.
-size_t staged_status_offset(int M, int N, int K, int S);
+size_t staged_status_offset(int M, int N, int K, int S, bool shared_b = false);
 // Test hooks of the bounded waits (process-wide; wait_polls <= 0 and announce_extra <= 0 restore the defaults).
 void staged_test_hooks(int wait_polls, int announce_extra);
 // Text of the last CUDA runtime error seen by this thread inside the library; returns MMB200_ERR_LAUNCH.

@@ -905,15 +905,22 @@ template <int NFMA, int FA, int FB>
 cudaError_t launch_staged_fmt(const Params& p, cudaStream_t stream, int* launches) {
   constexpr bool E4PAIR = FA == MMB200_FMT_E4M3 && FB == MMB200_FMT_E4M3;
   const bool tc = E4PAIR && !p.no_tensor_epass;
-  if (tc) predecode_tc_kernel<true><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_m), THREADS, 0, stream>>>(p);
-  else predecode_kernel<FA, FB, true><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_m), THREADS, 0, stream>>>(p);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
-  if (tc) predecode_tc_kernel<false><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_n), THREADS, 0, stream>>>(p);
-  else predecode_kernel<FA, FB, false><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_n), THREADS, 0, stream>>>(p);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) return err;
-  *launches += 2;
+  cudaError_t err = cudaSuccess;
+  if (!p.only_b) {
+    if (tc) predecode_tc_kernel<true><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_m), THREADS, 0, stream>>>(p);
+    else predecode_kernel<FA, FB, true><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_m), THREADS, 0, stream>>>(p);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    *launches += 1;
+  }
+  if (p.only_b || !p.shared_b) {                 // a shared B area was decoded by an earlier launch
+    if (tc) predecode_tc_kernel<false><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_n), THREADS, 0, stream>>>(p);
+    else predecode_kernel<FA, FB, false><<<dim3((unsigned)p.k_tiles, (unsigned)p.tiles_n), THREADS, 0, stream>>>(p);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    *launches += 1;
+  }
+  if (p.only_b) return cudaSuccess;
   if constexpr (E4PAIR) {
     if (tc) return launch_staged_main<NFMA, FA, FB, true>(p, stream, launches);
   }
@@ -969,7 +976,7 @@ struct WorkspaceLayout {
   int tiles_m, tiles_n, k_tiles;
 };
 // Offsets of the scratch memory. The layout without K slices is a prefix of the one with them.
-WorkspaceLayout workspace_layout(int M, int N, int K, int S, bool with_slices) {
+WorkspaceLayout workspace_layout(int M, int N, int K, int S, bool with_slices, bool shared_b = false) {
   WorkspaceLayout w;
   w.tiles_m = (M + BM - 1) / BM;
   w.tiles_n = (N + BN - 1) / BN;
@@ -981,7 +988,7 @@ WorkspaceLayout workspace_layout(int M, int N, int K, int S, bool with_slices) {
   constexpr size_t B_TILE = sizeof(TileB) > sizeof(TileTC) ? sizeof(TileB) : sizeof(TileTC);
   w.a = 0;
   w.b = w.a + (size_t)w.tiles_m * w.k_tiles * A_TILE;
-  w.flag_a = w.b + (size_t)w.tiles_n * w.k_tiles * B_TILE;
+  w.flag_a = w.b + (shared_b ? 0 : (size_t)w.tiles_n * w.k_tiles * B_TILE);   // B's tiles live in the shared area then
   w.flag_b = w.flag_a + (size_t)w.tiles_m * BM * sizeof(int);
   w.status = w.flag_b + (size_t)w.tiles_n * BN * sizeof(int);
   w.seq = w.status + 256;
@@ -1028,14 +1035,43 @@ cudaError_t launch_fast(const Params& p_in, int nfma, cudaStream_t stream) {
   return dispatch_formats(p, nfma, stream, false, &launches);
 }
 
-size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices) {
+size_t staged_workspace_bytes(int M, int N, int K, int S, bool with_slices, bool shared_b) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return workspace_layout(M, N, K, S < 1 ? 1 : S, with_slices).total;
+  return workspace_layout(M, N, K, S < 1 ? 1 : S, with_slices, shared_b).total;
 }
 
-size_t staged_status_offset(int M, int N, int K, int S) {
+size_t staged_status_offset(int M, int N, int K, int S, bool shared_b) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  return workspace_layout(M, N, K, S < 1 ? 1 : S, false).status;
+  return workspace_layout(M, N, K, S < 1 ? 1 : S, false, shared_b).status;
+}
+
+namespace {
+// Shared B area: tile images, then the column flags.
+size_t shared_b_flags_offset(int N, int K) {
+  const WorkspaceLayout w = workspace_layout(1, N, K, 1, false);
+  return (w.flag_a - w.b + 255) / 256 * 256;
+}
+}  // namespace
+size_t staged_shared_b_bytes(int N, int K) {
+  if (N <= 0 || K <= 0) return 0;
+  return shared_b_flags_offset(N, K) + ((size_t)((N + BN - 1) / BN) * BN * sizeof(int) + 255) / 256 * 256;
+}
+
+cudaError_t launch_predecode_b(const Params& p_in, int nfma, cudaStream_t stream, int* launches) {
+  Params p = p_in;
+  if (!p.shared_b || (reinterpret_cast<uintptr_t>(p.shared_b) & 127)) return cudaErrorInvalidValue;
+  const WorkspaceLayout w = workspace_layout(1, p.N, p.K, 1, false);
+  p.tiles_m = 0; p.tiles_n = w.tiles_n; p.k_tiles = w.k_tiles;
+  p.ws_b = p.shared_b;
+  p.ws_flag_b = reinterpret_cast<int*>(p.shared_b + shared_b_flags_offset(p.N, p.K));
+  p.only_b = 1;
+  {
+    const char* env = std::getenv("MMAEMU_B200_TC_EPASS");
+    if (env && env[0] == '0' && env[1] == 0) p.no_tensor_epass = 1;
+  }
+  cudaError_t err = cudaMemsetAsync(p.ws_flag_b, 0, (size_t)w.tiles_n * BN * sizeof(int), stream);
+  if (err != cudaSuccess) return err;
+  return dispatch_formats(p, nfma, stream, true, launches);
 }
 
 namespace {
@@ -1049,7 +1085,9 @@ void staged_test_hooks(int wait_polls, int announce_extra) {
 cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                           int* launches) {
   Params p = p_in;
-  WorkspaceLayout w = workspace_layout(p.M, p.N, p.K, p.S, false);
+  const bool shared_b = p.shared_b != nullptr;
+  if (shared_b && (reinterpret_cast<uintptr_t>(p.shared_b) & 127)) return cudaErrorInvalidValue;
+  WorkspaceLayout w = workspace_layout(p.M, p.N, p.K, p.S, false, shared_b);
   if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 127)) return cudaErrorInvalidValue;
   if ((long long)w.tiles_m * w.tiles_n > 0x7FFFFFFFLL || w.tiles_m > 65535 || w.tiles_n > 65535) return cudaErrorInvalidValue;
   const Plan plan = make_plan(p.K, p.fast, p.S, p.scheme);
@@ -1057,7 +1095,7 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
   p.slices = 1;
   std::vector<uint32_t> seq;
   {
-    const WorkspaceLayout wx = workspace_layout(p.M, p.N, p.K, p.S, true);
+    const WorkspaceLayout wx = workspace_layout(p.M, p.N, p.K, p.S, true, shared_b);
     const char* env = std::getenv("MMAEMU_B200_SLICES");           // "0": never slice (tests of the unsliced walkers)
     const bool allowed = !(env && env[0] == '0' && env[1] == 0);
     if (allowed && wx.chains_bytes && workspace_bytes >= wx.total && (p.S > 1 || !p.fast)) {
@@ -1083,6 +1121,11 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
   p.ws_b = base + w.b;
   p.ws_flag_a = reinterpret_cast<int*>(base + w.flag_a);
   p.ws_flag_b = reinterpret_cast<int*>(base + w.flag_b);
+  if (shared_b) {                                                // decoded by launch_predecode_b
+    p.ws_b = p.shared_b;
+    p.ws_flag_b = reinterpret_cast<int*>(p.shared_b + shared_b_flags_offset(p.N, p.K));
+  }
+  p.only_b = 0;
   p.status = reinterpret_cast<int*>(base + w.status);
   p.plan_group = plan.group;
   p.wait_polls = g_wait_polls.load();

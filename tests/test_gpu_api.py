@@ -364,3 +364,46 @@ def test_a_wait_that_runs_out_is_reported_and_nothing_is_written():
     assert L.mmb200_workspace_status(ws.data_ptr(), M, N, K, 1, stream) == _lib.OK
     want = oracle.scaled_mm(a.cpu().numpy(), b.cpu().numpy(), 0.5, 2.0, out="bfloat16", preset=32, fast=True)
     assert np.array_equal(D.cpu().numpy().view(np.uint16), want)
+
+
+@pytest.mark.parametrize("pipeline", ("1", "0"))
+def test_scaled_mm_host_slabs_equal_the_single_launch(pipeline, monkeypatch):
+    """Host operands in, host result out (mmb200_scaled_mm_host): calls large enough to be cut into row slabs that
+    overlap copies and kernels on internal streams must give the bits of the oracle and of scaled_mm on device
+    tensors -- ragged last slab, NaN codes in a late slab and in B, a split-K plan of the whole call, pinned and
+    pageable host memory, a padded out= -- and the same with the slabs turned off."""
+    monkeypatch.setenv("MMAEMU_B200_HOST_PIPELINE", pipeline)
+    M, N, K = 4200, 2048, 512                            # 33 x 16 output tiles: four slabs of 1024 rows and one of 104
+    rng = np.random.default_rng(77)
+    a = datagen.codes(rng, M, K, "e4m3", "gauss40")
+    b = datagen.codes(rng, N, K, "e4m3", "all_codes")
+    a[4150, 17], a[100, 3], b[2000, 500] = 0x7F, 0xFF, 0x7F
+    ta, tb = torch.from_numpy(a).view(F8["e4m3"]), torch.from_numpy(b).view(F8["e4m3"])
+    sa, sb = torch.tensor(0.75), torch.tensor(1.5)
+    want = oracle.scaled_mm(a, b, 0.75, 1.5, out="bfloat16", preset="hopper", fast=False)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        y = mm.scaled_mm_host(ta.pin_memory(), tb.pin_memory().t(), sa, sb, out_dtype=torch.bfloat16, profile="hopper",
+                              splitk=1)
+        assert y.device.type == "cpu" and np.array_equal(bits(y), want)
+        y = mm.scaled_mm_host(ta, tb.t(), sa, sb, out_dtype=torch.bfloat16, profile="hopper", splitk=1)   # pageable
+        assert np.array_equal(bits(y), want)
+        # a split-K plan (decided for the whole call, handed to every slab), fp8 output with scale_result, out= with a
+        # padded leading dimension, and twice in a row (the staging pool and the internal streams are reused)
+        sr = torch.tensor(0.5)
+        big = torch.zeros((M, N + 64), dtype=torch.float8_e4m3fn).pin_memory()
+        dev_y = mm.scaled_mm(ta.to(DEV), tb.to(DEV).t(), sa.to(DEV), sb.to(DEV), scale_result=sr.to(DEV),
+                             out_dtype=torch.float8_e4m3fn, use_fast_accum=True, profile="hopper",
+                             splitk=(2, "contiguous"))
+        for _ in range(2):
+            out = mm.scaled_mm_host(ta.pin_memory(), tb.pin_memory().t(), sa, sb, scale_result=sr,
+                                    out_dtype=torch.float8_e4m3fn, use_fast_accum=True, profile="hopper",
+                                    splitk=(2, "contiguous"), out=big[:, :N])
+            assert out.data_ptr() == big.data_ptr() and np.array_equal(bits(out), bits(dev_y))
+        assert not big[:, N:].view(torch.uint8).any()
+        # formats and presets the staged kernels do not serve take the one-launch path of the same entry point
+        a5 = datagen.codes(rng, 300, 192, "e5m2", "gauss40")
+        y = mm.scaled_mm_host(torch.from_numpy(a5).view(F8["e5m2"]), tb[:160, :192].t(), sa, sb,
+                              out_dtype=torch.float16, use_fast_accum=True, profile="b200-mma-sync-experimental", splitk=1)
+    assert np.array_equal(bits(y), oracle.scaled_mm(a5, b[:160, :192], 0.75, 1.5, out="float16", fmt_a="e5m2",
+                                                    preset=288, fast=True))

@@ -219,3 +219,28 @@ def test_presets():
     for bad in ((get_preset("ada"), 4, "contiguous"), (get_preset("hopper"), 2, "serial"), (get_preset("ada"), 2, "x")):
         with pytest.raises(ValueError):
             check_plan(bad[0], 64, bad[1], bad[2])
+
+
+def test_scaled_mm_host_validates_like_scaled_mm():
+    """The host-buffer entry point checks the call from metadata in scaled_mm's order before it touches a device."""
+    a, bt, sa, sb = ops()
+    assert "scaled_mm_host" in mm.__all__
+    y = mm.scaled_mm_host(a[:0], bt, sa, sb, out_dtype=torch.bfloat16)                 # zero-size result: no device needed
+    assert y.shape == (0, 48) and y.dtype == torch.bfloat16
+    y = mm.scaled_mm_host(a[:, :0], bt[:0], sa, sb, out_dtype=torch.float16)           # K == 0: +0 everywhere
+    assert y.shape == (32, 48) and not y.any()
+    with pytest.raises(mm.ReferenceRejectsError):
+        mm.scaled_mm_host(a.to(E5), bt.to(E5), sa, sb, out_dtype=torch.bfloat16, splitk=1)
+    with pytest.raises(mm.ReferenceRejectsError):
+        mm.scaled_mm_host(a, bt.t().contiguous().t().contiguous(), sa, sb, out_dtype=torch.bfloat16, splitk=1)   # row-major mat2
+    with pytest.raises(mm.UnsupportedFeatureError):
+        mm.scaled_mm_host(a, bt, torch.full((32, 1), 1.0), torch.full((1, 48), 1.0), out_dtype=torch.bfloat16)
+    with pytest.raises(mm.SplitKUnknownError):
+        mm.scaled_mm_host(a, bt, sa, sb, out_dtype=torch.bfloat16, profile="hopper-experimental")
+    with pytest.raises(ValueError, match="out must be"):
+        mm.scaled_mm_host(a, bt, sa, sb, out_dtype=torch.bfloat16, splitk=1, out=torch.empty(32, 47, dtype=torch.bfloat16))
+    with pytest.raises(mm.UnsupportedFeatureError, match="slow accumulation"):
+        mm.scaled_mm_host(a, bt, sa, sb, out_dtype=torch.bfloat16, splitk=1, profile="b200-mma-sync-experimental")
+    if not torch.cuda.is_available():
+        with pytest.raises(mm.BackendUnavailableError):
+            mm.scaled_mm_host(a, bt, sa, sb, out_dtype=torch.bfloat16, splitk=1)
