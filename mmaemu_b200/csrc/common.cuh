@@ -47,6 +47,8 @@ struct Params {
   // decodes B nor clears its flags. only_b: decode B into shared_b and launch nothing else.
   unsigned char* shared_b;
   int only_b;
+  int few_rows;          // at most 16 rows and no quantise prologue: the staged launch uses the kernels that decode both
+                         // operands themselves (set by the launcher)
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
   // multi-GPU assembly: the same output element is also stored at the same index of every peer_D[i] (device pointers
   // into other GPUs' memory, mapped into this process), so that every GPU ends up with the whole result

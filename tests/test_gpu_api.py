@@ -211,7 +211,7 @@ def test_backend_object_chain_fn():
 
 def test_launch_accounting():
     from mmaemu_b200 import _lib
-    a, b, ta, tb = operands(16, 16, 64, seed=7)
+    a, b, ta, tb = operands(48, 16, 64, seed=7)
     n0 = _lib.launch_count()
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
     assert _lib.launch_count() == n0 + 3              # two pre-decode kernels and the GEMM kernel (scratch memory path)
@@ -221,9 +221,18 @@ def test_launch_accounting():
     assert _lib.launch_count() == n0 + 8              # split plan: pre-decode x 2, the tile order, the GEMM kernel
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"), backend="cuda:b200-direct")
     assert _lib.launch_count() == n0 + 9              # without scratch memory split plans run on the integer kernel
-    a, b, ta, tb = operands(16, 16, 512, seed=8)
+    a, b, ta, tb = operands(48, 16, 512, seed=8)
     mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
     assert _lib.launch_count() == n0 + 14             # few tiles, 4 chains: pre-decode x 2, tile order, K slices, combine
+    # at most 16 rows: the kernels decode both operands themselves, so the pre-decode launches disappear
+    a, b, ta, tb = operands(16, 16, 512, seed=9)
+    n0 = _lib.launch_count()
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
+    assert _lib.launch_count() == n0 + 1              # the GEMM kernel alone
+    mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
+    assert _lib.launch_count() == n0 + 4              # tile order, K slices, combine
+    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"))
+    assert _lib.launch_count() == n0 + 7              # a split plan in K slices: tile order, K slices, combine
 
 
 def test_call_is_capturable_in_a_cuda_graph():
