@@ -51,11 +51,12 @@ STRONG = dict(name="cfg5_recipe_16384x16384x8192", profile="hopper", M=16384, N=
 # (smsp__inst_executed.sum * 32 / (M*N*K), profiles/): keyed by (kernel, products per block, accumulation). A workload
 # whose kernel has no capture gets no issue-slot roofline (null), never another kernel's constant.
 INST_PER_MAC = {("staged_tc_kernel", 32, "slow"): 2.514,       # 4096 cube, profiles/staged_tc_kernel_hopper_e4m3_2048cube.md
-                ("staged_kernel", 32, "slow"): 3.22,           # 2048 cube e5m2 x e4m3, profiles/staged_kernel_hopper_e5m2xe4m3_2048cube.md
-                ("fast_kernel", 32, "slow"): 3.43,             # 2048 cube, profiles/fast_kernel_hopper_e4m3_2048cube.md
-                ("integer_kernel", 32, "slow"): 8.5}           # 2048 cube, profiles/integer_kernel_hopper_e4m3_2048cube.md
+                ("staged_kernel", 32, "slow"): 3.16,           # 2048 cube e5m2 x e4m3, profiles/staged_kernel_hopper_e5m2xe4m3_2048cube.md
+                ("fast_kernel", 32, "slow"): 3.37,             # 2048 cube, profiles/fast_kernel_hopper_e4m3_2048cube.md
+                ("staged_kernel, at most 16 rows", 32, "slow"): 5.18,   # 16 x 4096 x 8192, profiles/few_rows_kernel_hopper_e5m2xe4m3_16x4096x8192.md
+                ("integer_kernel", 32, "slow"): 8.56}           # 2048 cube, profiles/integer_kernel_hopper_e4m3_2048cube.md
 # DRAM bytes per launch of the main kernel on the headline workload, one-pass ncu capture at full size
-# (dram__bytes_read.sum + dram__bytes_write.sum = 873,409,280 + 32,450,560; same profile file).
+# (dram__bytes_read.sum + dram__bytes_write.sum = 873,141,504 + 32,601,856; same profile file).
 DRAM_TRAFFIC = {("staged_tc_kernel", 32, "slow", 4096, 4096, 4096): 905743360}
 
 
@@ -313,7 +314,9 @@ def workload_text(c) -> str:
 
 def kernel_of(cfg, S=1) -> str:
     """Name of the main kernel the automatic choice runs for a configuration (with scratch memory)."""
-    return "staged_tc_kernel" if (cfg["fa"], cfg["fb"]) == ("e4m3", "e4m3") else "staged_kernel"
+    name = "staged_tc_kernel" if (cfg["fa"], cfg["fb"]) == ("e4m3", "e4m3") else "staged_kernel"
+    # with at most 16 rows (unsplit plans and K slices) the instantiations that decode both operands themselves run
+    return name + ", at most 16 rows" if cfg["M"] <= 16 else name
 
 
 class Timer:
@@ -726,9 +729,15 @@ def run_multi_gpu(args) -> int:
     a_pin, bt_pin = a_dev.view(torch.uint8).cpu().pin_memory(), bt_dev.view(torch.uint8).cpu().pin_memory()
     out_pin = torch.empty((m1 - m0, N), dtype=od).pin_memory()
 
+    from mmaemu_b200.sharding import gather_rows
+    b0, b1 = shard_rows(N, world, rank)
+    bt_pin_own = bt_pin[b0:b1]
+
     def step_e2e():
+        # every input byte crosses the host link once per job: this rank's rows of A, and its 1 / world of B's rows,
+        # which one all-gather over NVLink then completes on every GPU
         ad = a_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
-        bd = bt_pin.to(dev, non_blocking=True).view(torch.float8_e4m3fn)
+        bd = gather_rows(bt_pin_own.to(dev, non_blocking=True), N).view(torch.float8_e4m3fn)
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
             y = sharded_scaled_mm(ad, bd.t(), sa_dev, sb_dev, **kw)
@@ -844,10 +853,12 @@ def run_multi_gpu(args) -> int:
             "assembly_exposed_ms_per_step": ms - compute_ms / args.steps,
             "gate": gate,
             "e2e": {"value": 2.0 * macs / (e2e_ms / args.steps / 1e3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": ((m1 - m0) + N) * K, "d2h_bytes_per_step": (m1 - m0) * N * es,
+                    "h2d_bytes_per_step": ((m1 - m0) + (b1 - b0)) * K, "d2h_bytes_per_step": (m1 - m0) * N * es,
                     "ms_per_step": e2e_ms / args.steps,
-                    "call": "mmaemu_b200.sharded_scaled_mm on this rank's rows of A and all of B copied from pinned host "
-                            "memory each step (bytes per rank), this rank's rows of the assembled result copied back"},
+                    "call": "mmaemu_b200.sharded_scaled_mm on this rank's rows of A and its 1/N of B's rows copied from "
+                            "pinned host memory each step (bytes per rank; mmaemu_b200.sharding.gather_rows completes B "
+                            "on every GPU with one all-gather over NVLink), this rank's rows of the assembled result "
+                            "copied back"},
             "gpu_launches": int(launches), "clocks": clocks,
             "row_poor_grid": {"workload": f"hopper-te, {gM} x {gN} x {gK}, e5m2 x e4m3 -> bfloat16, slow accumulation, "
                                           f"split-K from the table; column groups 1 x {world}, every GPU ends up with "

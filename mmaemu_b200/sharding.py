@@ -150,6 +150,32 @@ def _peer_mode_available(device, group) -> bool:
     return good
 
 
+def gather_rows(local, full_rows: int, group=None):
+    """The whole row-sharded tensor on every rank: `local` holds this rank's rows [m0, m1) of shard_rows(full_rows, world,
+    rank) (for instance the rows of mat2.t() that this rank has just copied from the host); one all-gather over the
+    group's backend (NCCL over NVLink on CUDA ranks) assembles all of them. With it a replicated operand crosses the
+    host link once per job instead of once per rank. FP8 tensors travel as bytes."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    m0, m1 = shard_rows(full_rows, world, rank)
+    if local.shape[0] != m1 - m0:
+        raise ValueError(f"rank {rank} owns rows [{m0}, {m1}) but was given {local.shape[0]} rows")
+    if world == 1:
+        return local
+    per = shard_rows(full_rows, world, 0)[1]
+    cols = tuple(local.shape[1:])
+    row_bytes = local.element_size()
+    for extent in cols:
+        row_bytes *= extent
+    pad = torch.zeros((per, row_bytes), dtype=torch.uint8, device=local.device)
+    if m1 > m0:
+        pad[: m1 - m0] = local.contiguous().view(torch.uint8).view(m1 - m0, row_bytes)
+    full = torch.empty((world * per, row_bytes), dtype=torch.uint8, device=local.device)
+    dist.all_gather_into_tensor(full.view(-1), pad.view(-1), group=group)
+    return full[:full_rows].view(local.dtype).view((full_rows,) + cols)
+
+
 def sharded_scaled_mm(input, mat2, scale_a, scale_b, bias=None, scale_result=None, out_dtype=None,
                       use_fast_accum=False, *, profile=None, splitk="auto", backend="auto", group=None, gather=True,
                       compute=None, input_is_local=False, full_rows=None, mat2_is_local=False, full_cols=None,

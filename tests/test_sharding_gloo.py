@@ -202,3 +202,41 @@ def test_a_rejected_call_is_rejected_on_every_rank(case):
         assert p.exitcode == 0
     results = sorted(q.get(timeout=5) for _ in range(2))
     assert [r[1] for r in results] == [True, True], results
+
+
+def _worker_gather(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from mmaemu_b200.sharding import gather_rows, shard_rows
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = True
+        for rows, dtype in ((300, torch.float8_e4m3fn), (100, torch.float8_e5m2), (256, torch.bfloat16)):
+            g = torch.Generator().manual_seed(rows)
+            full = torch.randn(rows, 48, generator=g).to(dtype)
+            m0, m1 = shard_rows(rows, world, rank)                 # 100 rows on two ranks: rank 1 owns nothing
+            got = gather_rows(full[m0:m1].clone(), rows)
+            ok = ok and got.dtype == dtype and got.shape == full.shape and bool(
+                torch.equal(got.view(torch.uint8), full.view(torch.uint8)))
+        try:
+            gather_rows(full[:1], 256)
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_rows_assembles_a_row_sharded_operand():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_gather, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert sorted(q.get(timeout=5) for _ in range(2)) == [(0, True), (1, True)]
