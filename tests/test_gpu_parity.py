@@ -148,6 +148,34 @@ def test_nonfinite_inputs_and_output_dtypes(gpu, fmts, out, kernel):
         _same(gpu.scaled_mm(a, b, scale, 1.7, kernel=kernel, **kw), oracle.scaled_mm(a, b, scale, 1.7, **kw), out)
 
 
+@pytest.mark.parametrize("kernel", ("auto", "staged", "staged-whole"))
+@pytest.mark.parametrize("fmts", (("e4m3", "e4m3"), ("e5m2", "e4m3"), ("e4m3", "e5m2"), ("e5m2", "e5m2")), ids="x".join)
+def test_at_most_16_rows(gpu, fmts, kernel):
+    """Calls with at most 16 rows run on kernels of their own (both operands decoded in the kernel, all warps on the 16
+    rows, K slices for plans with several chains): every row count's edge, ragged column counts, padded leading
+    dimensions, non-finite codes in both operands -- also where only one K slice sees them -- every output dtype,
+    slow and fast accumulation, a split plan."""
+    rng = np.random.default_rng(zlib.crc32(repr(fmts).encode()))
+    outs = ("float32", "bfloat16", "float16", "float8_e4m3fn", "float8_e5m2")
+    n = 0
+    for M in (1, 7, 16):
+        for N, K in ((40, 48), (300, 2048), (128, 4096)):
+            a = datagen.codes(rng, M, K, fmts[0], "gauss40")
+            b = datagen.codes(rng, N, K, fmts[1], "all_codes")
+            nan_a, nan_b = (0x7F if fmts[0] == "e4m3" else 0x7E), (0x7F if fmts[1] == "e4m3" else 0x7C)   # NaN; NaN or +Inf
+            a[M - 1, K - 3] = nan_a                                   # seen by the last K slice only
+            b[N // 2, 5] = nan_b | 0x80                               # seen by the first one only
+            if fmts[0] == "e5m2" and M > 1:
+                a[0, K // 2] = 0x7C                                   # +Inf: the IEEE class needs the walk over K
+            for fast, S, scheme in ((False, 1, "none"), (True, 1, "none"), (True, 3, "contiguous")):
+                out = outs[n % 5]
+                n += 1
+                kw = dict(out=out, fmt_a=fmts[0], fmt_b=fmts[1], preset=32, fast=fast, S=S, scheme=scheme,
+                          scale_result=1.5 if out.startswith("float8") else None)
+                _same(gpu.scaled_mm(a, b, 0.02, 0.7, kernel=kernel, ld_pad=16 * (n % 2), **kw),
+                      oracle.scaled_mm(a, b, 0.02, 0.7, **kw), f"{M}x{N}x{K} {out} fast={fast} S={S}")
+
+
 @pytest.mark.parametrize("kernel", KERNELS)
 def test_every_byte_value_and_padded_leading_dimensions(gpu, kernel):
     rng = np.random.default_rng(5)
