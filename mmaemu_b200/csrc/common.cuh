@@ -47,8 +47,10 @@ struct Params {
   // decodes B nor clears its flags. only_b: decode B into shared_b and launch nothing else.
   unsigned char* shared_b;
   int only_b;
-  int few_rows;          // at most 16 rows and no quantise prologue: the staged launch uses the kernels that decode both
-                         // operands themselves (set by the launcher)
+  int few_rows;          // the staged launch uses the kernels that work on 16 rows per CTA and decode both operands
+                         // themselves (set by the launcher: calls with at most 16 rows, and calls whose 128 x 128 output
+                         // tiles and chains would leave most SMs idle)
+  int row_groups;        // 16-row groups per 128-row tile in that case (grid z): 1 or 8
   int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
   // multi-GPU assembly: the same output element is also stored at the same index of every peer_D[i] (device pointers
   // into other GPUs' memory, mapped into this process), so that every GPU ends up with the whole result
@@ -248,12 +250,13 @@ struct Epilogue {
     else if (es == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)b;
     else *dst = (uint8_t)b;
   }
+  // `rows`: how many rows of the image (from its first) were parked
   __device__ __forceinline__ void flush(const Params& p, const unsigned char* tile, int m0, int n0, int tid,
-                                        int nthreads) const {
+                                        int nthreads, int rows = TILE_DIM) const {
     const int es = elem_size(), pitch = tile_pitch(), per_row = TILE_DIM * es / 16, per_piece = 16 / es;
     bool vec = (reinterpret_cast<uintptr_t>(p.D) % 16 == 0) && ((p.ldd * es) % 16 == 0);
     for (int q = 0; q < n_peers; ++q) vec = vec && (reinterpret_cast<uintptr_t>(peers[q]) % 16 == 0);
-    for (int idx = tid; idx < TILE_DIM * per_row; idx += nthreads) {
+    for (int idx = tid; idx < rows * per_row; idx += nthreads) {
       const int row = idx / per_row, piece = idx % per_row, gm = m0 + row, gn = n0 + piece * per_piece;
       if (gm >= p.M || gn >= p.N) continue;
       const unsigned char* src = tile + row * pitch + piece * 16;

@@ -29,16 +29,26 @@ def _dev(x):
 
 
 def _ws(L, M, N, K, kernel, S=1):
-    """Scratch memory for the staged kernels when `kernel` is 'staged', 'staged-whole' or 'staged-int' (test-side
-    names: automatic choice + workspace; '-whole' turns K slicing off, so that few-tile shapes run the one-pass plan
-    walkers; '-int' keeps the exponent pass of E4M3 x E4M3 on the CUDA cores instead of the tensor cores)."""
+    """Scratch memory for the staged kernels when `kernel` is 'staged', 'staged-whole', 'staged-int' or 'staged-rows'
+    (test-side names: automatic choice + workspace; '-whole' turns K slicing off, so that few-tile shapes run the
+    one-pass plan walkers; '-int' keeps the exponent pass of E4M3 x E4M3 on the CUDA cores instead of the tensor cores;
+    '-rows' lets shapes with few output tiles run on the 16-row kernels, as the library does by default)."""
     os.environ["MMAEMU_B200_SLICES"] = "0" if kernel == "staged-whole" else "1"
     os.environ["MMAEMU_B200_TC_EPASS"] = "0" if kernel == "staged-int" else "1"
-    if kernel not in ("staged", "staged-whole", "staged-int"):
+    # small shapes would all go to the 16-row kernels: only 'staged-rows' lets them ('staged*' otherwise keep the
+    # 8-row-slot kernels under test; calls of at most 16 rows use the 16-row kernels either way)
+    os.environ["MMAEMU_B200_ROW_GROUPS"] = "1" if kernel == "staged-rows" else "0"
+    if kernel not in ("staged", "staged-whole", "staged-int", "staged-rows"):
         return None, None, 0, kernel
     n = int(L.mmb200_workspace_bytes_split(M, N, K, S))
     ws = torch.empty(max(n, 1), dtype=torch.uint8, device=DEV)
     return ws, ws.data_ptr(), n, "auto"
+
+
+def _env_reset():
+    """The launch has read the switches: later calls in this process (the Python entry points) see the defaults."""
+    for name in ("MMAEMU_B200_SLICES", "MMAEMU_B200_TC_EPASS", "MMAEMU_B200_ROW_GROUPS"):
+        os.environ.pop(name, None)
 
 
 def scaled_mm(a, b, scale_a, scale_b, *, out="bfloat16", fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=False, S=1,
@@ -59,6 +69,7 @@ def scaled_mm(a, b, scale_a, scale_b, *, out="bfloat16", fmt_a="e4m3", fmt_b="e4
                                int(bool(fast)), int(S), _lib.SCHEME_CODES[scheme], sc.data_ptr(), sc.data_ptr() + 4,
                                None if scale_result is None else sc.data_ptr() + 8, _lib.KERNEL_CODES[kernel], ws_ptr,
                                ws_bytes, _stream())
+    _env_reset()
     _lib.check("mmb200_scaled_mm_ws", rc)
     torch.cuda.synchronize(DEV)
     return D[:, :N].cpu().numpy().view(OUT_NP[out])
@@ -75,13 +86,14 @@ def accumulate(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, fast=True, S=1, s
                                 _lib.FMT_CODES[fmt_b], C.data_ptr(), max(N, 1), M, N, K, int(preset), int(bool(fast)),
                                 int(S), _lib.SCHEME_CODES[scheme], _lib.KERNEL_CODES[kernel], ws_ptr, ws_bytes,
                                 _stream())
+    _env_reset()
     _lib.check("mmb200_accumulate_ws", rc)
     torch.cuda.synchronize(DEV)
     return C[:, :N].cpu().numpy().view(np.uint32)
 
 
 def chain(a, b, *, fmt_a="e4m3", fmt_b="e4m3", preset=32, kernel="auto"):
-    if kernel in ("staged", "staged-whole", "staged-int"):     # the chain entry point has no workspace variant: fast plan, no patch
+    if kernel in ("staged", "staged-whole", "staged-int", "staged-rows"):     # the chain entry point has no workspace variant: fast plan, no patch
         clean = [np.where((x & 0x7F) == 0x7F, 0, x) if f == "e4m3" else np.where((x & 0x7C) == 0x7C, 0, x)
                  for x, f in ((a, fmt_a), (b, fmt_b))]
         return accumulate(clean[0].astype(np.uint8), clean[1].astype(np.uint8), fmt_a=fmt_a, fmt_b=fmt_b, preset=preset,

@@ -209,8 +209,9 @@ def test_backend_object_chain_fn():
     assert BACKEND.supports(SimpleNamespace(device="cpu", fmt_a="e4m3", fmt_b="e4m3", preset="ada")) is not None
 
 
-def test_launch_accounting():
+def test_launch_accounting(monkeypatch):
     from mmaemu_b200 import _lib
+    monkeypatch.setenv("MMAEMU_B200_ROW_GROUPS", "0")    # the 8-row-slot kernels and their pre-decode launches
     a, b, ta, tb = operands(48, 16, 64, seed=7)
     n0 = _lib.launch_count()
     mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
@@ -224,15 +225,18 @@ def test_launch_accounting():
     a, b, ta, tb = operands(48, 16, 512, seed=8)
     mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
     assert _lib.launch_count() == n0 + 14             # few tiles, 4 chains: pre-decode x 2, tile order, K slices, combine
-    # at most 16 rows: the kernels decode both operands themselves, so the pre-decode launches disappear
-    a, b, ta, tb = operands(16, 16, 512, seed=9)
-    n0 = _lib.launch_count()
-    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
-    assert _lib.launch_count() == n0 + 1              # the GEMM kernel alone
-    mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
-    assert _lib.launch_count() == n0 + 4              # tile order, K slices, combine
-    mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"))
-    assert _lib.launch_count() == n0 + 7              # a split plan in K slices: tile order, K slices, combine
+    # the 16-row kernels decode both operands themselves, so the pre-decode launches disappear: calls of at most 16
+    # rows always, and -- by default -- calls whose output tiles and chains would leave most SMs without a CTA
+    for M, env in ((16, "0"), (48, "1")):
+        monkeypatch.setenv("MMAEMU_B200_ROW_GROUPS", env)
+        a, b, ta, tb = operands(M, 16, 512, seed=9)
+        n0 = _lib.launch_count()
+        mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=1)
+        assert _lib.launch_count() == n0 + 1          # the GEMM kernel alone
+        mm.accumulate(ta, tb, use_fast_accum=False, profile="ada", splitk=1)
+        assert _lib.launch_count() == n0 + 4          # tile order, K slices, combine
+        mm.accumulate(ta, tb, use_fast_accum=True, profile="ada", splitk=(2, "serial"))
+        assert _lib.launch_count() == n0 + 7          # a split plan in K slices: tile order, K slices, combine
 
 
 def test_call_is_capturable_in_a_cuda_graph():
@@ -323,12 +327,13 @@ def test_quantised_activations_argument_checks():
     assert empty.shape == (0, 16)
 
 
-def test_a_wait_that_runs_out_is_reported_and_nothing_is_written():
+def test_a_wait_that_runs_out_is_reported_and_nothing_is_written(monkeypatch):
     """The scratch-memory kernels bound every wait for their bulk copies. The test hook makes the copies announce 16
     bytes more than they bring, so the barrier of the first stage never completes: the kernel must give up after the
     (shortened) bound, record the status word, leave D untouched and return -- no fault, no endless spin -- and the
     entry points that read the word must report MMB200_ERR_TIMEOUT. The next call, with the hook cleared, works."""
     L = _lib.load()
+    monkeypatch.setenv("MMAEMU_B200_ROW_GROUPS", "0")   # the kernels with the ring (the 16-row kernels have no waits)
     M, N, K = 256, 128, 512
     rng = np.random.default_rng(9)
     a = torch.from_numpy(datagen.codes(rng, M, K, "e4m3", "gauss40")).to(DEV)

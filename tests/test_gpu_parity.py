@@ -19,7 +19,7 @@ import golden_cases as G
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
-KERNELS = ("integer", "auto", "staged", "staged-whole")     # "staged*": with scratch memory (tests/gpu_runner.py)
+KERNELS = ("integer", "auto", "staged", "staged-whole", "staged-rows")     # "staged*": with scratch memory (tests/gpu_runner.py)
 
 
 @pytest.fixture(scope="module")
@@ -148,7 +148,7 @@ def test_nonfinite_inputs_and_output_dtypes(gpu, fmts, out, kernel):
         _same(gpu.scaled_mm(a, b, scale, 1.7, kernel=kernel, **kw), oracle.scaled_mm(a, b, scale, 1.7, **kw), out)
 
 
-@pytest.mark.parametrize("kernel", ("auto", "staged", "staged-whole"))
+@pytest.mark.parametrize("kernel", ("auto", "staged", "staged-whole", "staged-rows"))
 @pytest.mark.parametrize("fmts", (("e4m3", "e4m3"), ("e5m2", "e4m3"), ("e4m3", "e5m2"), ("e5m2", "e5m2")), ids="x".join)
 def test_at_most_16_rows(gpu, fmts, kernel):
     """Calls with at most 16 rows run on kernels of their own (both operands decoded in the kernel, all warps on the 16
