@@ -87,7 +87,9 @@ struct Lane {
     const int warp = tid / 32, lane = tid % 32;
     wm = few ? 0 : warp / 4; wn = warp % 4; q = lane / 4; u = lane % 4;
     half = few ? warp / 4 : -1;
-    arow0 = 64 * wm + q * 8;                 // permuted position of row slot 0; slot i is at arow0 + i
+    // permuted position of row slot 0; slot i is at arow0 + i. The 16-row kernels keep their 16 rows in the first 16
+    // positions (row q + 8 i at 2 q + i), so that a warp's loads of A touch 64 consecutive bytes instead of 256.
+    arow0 = few ? q * 2 : 64 * wm + q * 8;
     bcol0 = 32 * wn + u * 8;                 // permuted position of column slot 0
   }
   __device__ __forceinline__ bool owns(int j) const { return half < 0 || j / 4 == half; }
@@ -119,10 +121,10 @@ __device__ __forceinline__ void code_values(uint32_t ws, float (&val)[4]) {
 
 // Decodes 16 codes of one row (k = kk .. kk + 15 of the k-tile) into a tile; returns the non-finite classes seen.
 template <int FA, int FB, bool IS_A, typename Tile>
-__device__ __forceinline__ uint32_t decode16(const uint4 raw, Tile& tile, int row, int kk) {
+__device__ __forceinline__ uint32_t decode16(const uint4 raw, Tile& tile, int row, int kk, int pos_given = -1) {
   using P = fm::Pair<FA, FB>;
   constexpr int FMT = IS_A ? FA : FB;
-  const int pos = IS_A ? pos_a(row) : pos_b(row);
+  const int pos = pos_given >= 0 ? pos_given : (IS_A ? pos_a(row) : pos_b(row));
   const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t seen = 0;
 #pragma unroll
@@ -712,10 +714,10 @@ __global__ void __launch_bounds__(THREADS) predecode_kernel(const __grid_constan
 // Decodes 16 E4M3 codes of one row (k = 16 lhalf .. + 15 of the k-tile) into a tile of the tensor-core exponent pass;
 // returns the non-finite classes seen.
 template <bool IS_A>
-__device__ __forceinline__ uint32_t decode16_tc(const uint4 raw, TileTC& tile, int lrow, int lhalf) {
+__device__ __forceinline__ uint32_t decode16_tc(const uint4 raw, TileTC& tile, int lrow, int lhalf, int pos_given = -1) {
   constexpr int E4 = MMB200_FMT_E4M3;
   using P = fm::Pair<E4, E4>;
-  const int pos = IS_A ? pos_a(lrow) : pos_b(lrow);
+  const int pos = pos_given >= 0 ? pos_given : (IS_A ? pos_a(lrow) : pos_b(lrow));
   const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t seen = 0;
 #pragma unroll
@@ -921,6 +923,7 @@ __device__ __forceinline__ void few_rows_body(const Params& p, unsigned char* sm
   // loader: thread (lrow, lhalf) holds 16 codes of row lrow of B, and -- the first 16 rows -- of A
   const int lrow = tid % 128, lhalf = tid / 128;
   const bool a_row = lrow < 16;
+  const int a_pos = 2 * (lrow % 8) + lrow / 8;   // where struct Lane looks for row lrow of the group
   uint4 raw_a = make_uint4(0, 0, 0, 0), raw_b = make_uint4(0, 0, 0, 0);
   auto fetch = [&](int t) {
     const int kt = PLAN ? (int)(__ldg(p.ws_seq + t0 + t) & SEQ_TILE_MASK) : t;
@@ -933,10 +936,10 @@ __device__ __forceinline__ void few_rows_body(const Params& p, unsigned char* sm
     uint32_t cb, ca = 0;
     if constexpr (TC) {
       cb = decode16_tc<false>(raw_b, st.b, lrow, lhalf);
-      if (a_row) ca = decode16_tc<true>(raw_a, st.a, lrow, lhalf);
+      if (a_row) ca = decode16_tc<true>(raw_a, st.a, lrow, lhalf, a_pos);
     } else {
       cb = decode16<FA, FB, false>(raw_b, st.b, lrow, 16 * lhalf);
-      if (a_row) ca = decode16<FA, FB, true>(raw_a, st.a, lrow, 16 * lhalf);
+      if (a_row) ca = decode16<FA, FB, true>(raw_a, st.a, lrow, 16 * lhalf, a_pos);
     }
     if (cb) atomicOr(&p.ws_flag_b[n0 + lrow], (int)cb);
     if (ca) atomicOr(&p.ws_flag_a[m0 + lrow], (int)ca);
