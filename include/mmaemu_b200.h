@@ -137,7 +137,10 @@ size_t mmb200_workspace_bytes(int M, int N, int K);
  * less, split plans run on the integer kernel as they do without workspace. For shapes with few 128 x 128 output tiles the
  * size also covers the chain results of K-sliced execution (plans with several chains are spread over the SMs along K and
  * summed in the plan's order by a second kernel; up to 4 GiB, not used when the workspace is smaller or when
- * $MMAEMU_B200_SLICES is 0). */
+ * $MMAEMU_B200_SLICES is 0). Calls with at most 16 rows, and calls whose 128 x 128 output tiles and chains would leave
+ * most SMs without a CTA, run on kernels that work on 16 rows per CTA and decode both operands themselves (no
+ * pre-decode launches; $MMAEMU_B200_ROW_GROUPS=0 keeps them to calls of at most 16 rows). Same results bit for bit
+ * either way. */
 size_t mmb200_workspace_bytes_split(int M, int N, int K, int S);
 int mmb200_scaled_mm_ws(const void *A_dev, int64_t lda, int fmt_a, const void *B_dev, int64_t ldb, int fmt_b,
                         void *D_dev, int64_t ldd, int out_dtype, int M, int N, int K, int nfma, int fast, int S,
