@@ -246,10 +246,10 @@ def cpu_baseline(a, bt, sa, sb, cfg, seconds: float = 12.0) -> dict:
     ref = load_reference()
     flops_per_row = 2.0 * cfg["N"] * cfg["K"]
 
-    def measure(impl, budget):
+    def measure(impl, target_s):
         rows = 8
         probe = cpu_call(impl, a, bt, sa, sb, cfg, rows)
-        rows = int(max(8, min(a.shape[0], rows * budget / max(probe, 1e-3))))
+        rows = int(max(8, min(a.shape[0], rows * target_s / max(probe, 1e-3))))
         dt = cpu_call(impl, a, bt, sa, sb, cfg, rows)
         return {"value": rows * flops_per_row / dt / 1e12, "unit": "TFLOP/s (emulated, 2MNK/t)", "cores": cores,
                 "sample": f"first {rows} of {a.shape[0]} rows x all {cfg['N']} columns x K={cfg['K']}, {dt:.1f} s",
