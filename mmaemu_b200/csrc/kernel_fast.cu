@@ -77,6 +77,22 @@ struct TileTC {
 };
 static_assert(sizeof(TileTC) == 34816, "tile layout");
 
+// A's k-tile in the 16-row kernels: the same arrays with 16 positions (row q + 8 i of the group at 2 q + i), 5 KB
+// instead of 40, so that two CTAs share an SM.
+constexpr int FR = 16;
+struct TileA16 {
+  float v[KT][FR];
+  uint32_t x[KT][FR];
+  uint32_t t[KT / 4][FR];
+  uint32_t s[KT / 4][FR];
+};
+struct TileTC16 {
+  float v[KT][FR];
+  uint32_t t[KT / 4][FR];
+  uint32_t s[KT / 4][FR];
+  uint16_t e[FR][EP];
+};
+
 // The thread's place in the tile (see the mapping above).
 // With at most 16 rows (`few`: the kernels instantiated for two row slots) the warps of the second half would hold no
 // row of the problem, so both halves take the rows of the first one and share its columns instead: half 0 computes the
@@ -248,8 +264,8 @@ __device__ __forceinline__ void products_and_fix(float (&acc)[TM][TN], const uin
 
 // One block of NFMA products starting at k index c0 of the tiles with the CUDA-core E-pass: the columns J0 .. J0 + NJ - 1
 // of the thread's outputs.
-template <int NFMA, int FA, int FB, int J0, int TMI>
-__device__ __forceinline__ void block_strip(float (&acc)[TM][TN], const TileA& A, const TileB& B, int c0,
+template <int NFMA, int FA, int FB, int J0, int TMI, class TA_>
+__device__ __forceinline__ void block_strip(float (&acc)[TM][TN], const TA_& A, const TileB& B, int c0,
                                             const Lane& ln) {
   const int a_pos = ln.arow0, b_pos = ln.bcol0 + J0;
   // ---- E-pass: exponent field of 2^E_prod for every output, two outputs per packed add-max
@@ -315,8 +331,8 @@ __device__ __forceinline__ void mma_bf16_first(float (&d)[4], const uint32_t (&a
 // lies in [2^(8 E - 7), 2^(8 (E + 1) - 7)) whatever the accumulation order and truncation, so E is the sum's exponent
 // field shifted right by 3 (fast_math.cuh, block_exponent_pow). The sums come from mma.sync.m16n8k16 (bf16 inputs, fp32
 // accumulators in registers), two (hopper) or one (ada) per 16 x 8 output tile and block.
-template <int NFMA, int J0, int TMI>
-__device__ __forceinline__ void block_strip_tc(float (&acc)[TM][TN], const TileTC& A, const TileTC& B, int c0,
+template <int NFMA, int J0, int TMI, class TA_>
+__device__ __forceinline__ void block_strip_tc(float (&acc)[TM][TN], const TA_& A, const TileTC& B, int c0,
                                                const Lane& ln, int lane) {
   constexpr int E4 = MMB200_FMT_E4M3;
   constexpr int NI = NJ / 2, NP0 = J0 / 4, MI = TMI / 2;            // n-tiles of the strip; its first pair; m-tiles
@@ -356,8 +372,8 @@ __device__ __forceinline__ void block_strip_tc(float (&acc)[TM][TN], const TileT
 }
 
 // One block for all the thread's outputs, with either E-pass.
-template <int NFMA, int FA, int FB, int TMI>
-__device__ __forceinline__ void block_step(float (&acc)[TM][TN], const TileA& A, const TileB& B, int c0, const Lane& ln,
+template <int NFMA, int FA, int FB, int TMI, class TA_>
+__device__ __forceinline__ void block_step(float (&acc)[TM][TN], const TA_& A, const TileB& B, int c0, const Lane& ln,
                                            int) {
   if constexpr (TMI == 2 && STRIPS == 2) {   // few rows: each half of the warps computes one strip (warp-uniform)
     if (ln.half == 0) block_strip<NFMA, FA, FB, 0, TMI>(acc, A, B, c0, ln);
@@ -367,8 +383,8 @@ __device__ __forceinline__ void block_step(float (&acc)[TM][TN], const TileA& A,
   block_strip<NFMA, FA, FB, 0, TMI>(acc, A, B, c0, ln);
   if constexpr (STRIPS == 2) block_strip<NFMA, FA, FB, NJ, TMI>(acc, A, B, c0, ln);
 }
-template <int NFMA, int FA, int FB, int TMI>
-__device__ __forceinline__ void block_step(float (&acc)[TM][TN], const TileTC& A, const TileTC& B, int c0,
+template <int NFMA, int FA, int FB, int TMI, class TA_>
+__device__ __forceinline__ void block_step(float (&acc)[TM][TN], const TA_& A, const TileTC& B, int c0,
                                            const Lane& ln, int lane) {
   static_assert(FA == MMB200_FMT_E4M3 && FB == MMB200_FMT_E4M3, "the tensor-core E-pass serves E4M3 x E4M3");
   if constexpr (TMI == 2 && STRIPS == 2) {
@@ -713,8 +729,8 @@ __global__ void __launch_bounds__(THREADS) predecode_kernel(const __grid_constan
 
 // Decodes 16 E4M3 codes of one row (k = 16 lhalf .. + 15 of the k-tile) into a tile of the tensor-core exponent pass;
 // returns the non-finite classes seen.
-template <bool IS_A>
-__device__ __forceinline__ uint32_t decode16_tc(const uint4 raw, TileTC& tile, int lrow, int lhalf, int pos_given = -1) {
+template <bool IS_A, class Tile>
+__device__ __forceinline__ uint32_t decode16_tc(const uint4 raw, Tile& tile, int lrow, int lhalf, int pos_given = -1) {
   constexpr int E4 = MMB200_FMT_E4M3;
   using P = fm::Pair<E4, E4>;
   const int pos = pos_given >= 0 ? pos_given : (IS_A ? pos_a(lrow) : pos_b(lrow));
@@ -896,6 +912,19 @@ __device__ __forceinline__ void staged_body(const Params& p, unsigned char* smem
                         PLAN ? p.ws_tot + (size_t)blockIdx.x * (TM * TN * THREADS) : nullptr);
 }
 
+// Shared memory of the 16-row kernels: two stages of a compact tile of A and a tile of B (37 KB each), and the running
+// chain sums of the thread's 2 x 8 output slots for slow accumulation in one pass.
+template <bool TC> struct StageFew { TileA16 a; TileB b; };
+template <> struct StageFew<true> { TileTC16 a; TileTC b; };
+template <bool TC>
+struct SmemFew {
+  StageFew<TC> stage[2];
+  float part[2 * TN][THREADS];
+};
+template <bool TC> constexpr size_t smem_few(bool with_part) {
+  return with_part ? sizeof(SmemFew<TC>) : offsetof(SmemFew<TC>, part);
+}
+
 // The kernels for at most 16 rows (TMI = 2; struct Lane). There is one row of output tiles, so a decoded tile of B would
 // be read exactly once and a decoded tile of A holds 16 useful rows of 128: they read the codes of both operands
 // themselves and decode them into the stage -- all threads, one k-tile ahead of the arithmetic, with the codes of the
@@ -908,8 +937,8 @@ __device__ __forceinline__ void few_rows_body(const Params& p, unsigned char* sm
   constexpr int TMI = 2;
   static_assert(STRIPS == 2, "the 16-row kernels split the column strips between the two halves of the warps");
   constexpr bool PLAN = MODE != MODE_ORDER, SLICED = MODE == MODE_SLICED;
-  using Stage = StageOf<TC>;
-  SmemStaged<TC>& sm = *reinterpret_cast<SmemStaged<TC>*>(smem_raw);
+  using Stage = StageFew<TC>;
+  SmemFew<TC>& sm = *reinterpret_cast<SmemFew<TC>*>(smem_raw);
   const int tid = threadIdx.x;
   int tile_m, tile_n;
   tile_of_cta(p, (int)blockIdx.x, tile_m, tile_n);
@@ -950,7 +979,7 @@ __device__ __forceinline__ void few_rows_body(const Params& p, unsigned char* sm
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
       acc[i][j] = 0.0f;
-      if (SLOW && !SLICED) sm.part[i * TN + j][tid] = 0.0f;
+      if (SLOW && !SLICED && i < TMI) sm.part[i * TN + j][tid] = 0.0f;
     }
   if (T > 0) {
     fetch(0);
@@ -979,16 +1008,28 @@ __device__ __forceinline__ void few_rows_body(const Params& p, unsigned char* sm
 }
 
 template <int NFMA, int FA, int FB, bool SLOW, int MODE, int TMI>
-__global__ void __launch_bounds__(THREADS, 1) staged_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(THREADS, TMI == 2 ? 2 : 1) staged_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   if constexpr (TMI == 2) few_rows_body<NFMA, FA, FB, SLOW, MODE, false>(p, smem_raw);
   else staged_body<NFMA, FA, FB, SLOW, MODE, false, TMI>(p, smem_raw);
 }
 template <int NFMA, bool SLOW, int MODE, int TMI>
-__global__ void __launch_bounds__(THREADS, 1) staged_tc_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(THREADS, TMI == 2 ? 2 : 1) staged_tc_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   if constexpr (TMI == 2) few_rows_body<NFMA, MMB200_FMT_E4M3, MMB200_FMT_E4M3, SLOW, MODE, true>(p, smem_raw);
   else staged_body<NFMA, MMB200_FMT_E4M3, MMB200_FMT_E4M3, SLOW, MODE, true, TMI>(p, smem_raw);
+}
+
+// SMs of the current device (cached per device; 148 if the query fails).
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -1019,6 +1060,11 @@ cudaError_t launch_staged_main(const Params& p, cudaStream_t stream, int* launch
   const bool chains_in_split = p.plan_group != 0;            // slow accumulation: chains end inside a split
   const bool few_rows = p.few_rows != 0;
   auto go = [&](auto kern, size_t smem, unsigned slices) -> cudaError_t {
+    // Two CTAs of the 16-row kernels fit an SM. When the launch has no more working CTAs than the device has SMs, they
+    // should not share one (measured: 128 CTAs packed two per SM ran 1.5 times longer): asking for more than half of an
+    // SM's shared memory keeps them apart.
+    if (few_rows && (long long)p.tiles_n * ((p.M + 15) / 16) * slices <= sm_count() && smem < ((size_t)120 << 10))
+      smem = (size_t)120 << 10;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<dim3(tiles, slices, few_rows ? (unsigned)p.row_groups : 1u), THREADS, smem, stream>>>(p);
@@ -1028,10 +1074,11 @@ cudaError_t launch_staged_main(const Params& p, cudaStream_t stream, int* launch
 #define MMB_KERNEL(SLOW, MODE, TMI) \
   [&]() { if constexpr (TC) return staged_tc_kernel<NFMA, SLOW, MODE, TMI>; else return staged_kernel<NFMA, FA, FB, SLOW, MODE, TMI>; }()
   const size_t small = smem_staged<TC>(false), large = smem_staged<TC>(true);
+  const size_t small16 = smem_few<TC>(false), large16 = smem_few<TC>(true);      // the 16-row kernels: two CTAs per SM
   cudaError_t err;
   if (p.slices > 1) {
-    if (few_rows) err = chains_in_split ? go(MMB_KERNEL(true, MODE_SLICED, 2), small, (unsigned)p.slices)
-                                        : go(MMB_KERNEL(false, MODE_SLICED, 2), small, (unsigned)p.slices);
+    if (few_rows) err = chains_in_split ? go(MMB_KERNEL(true, MODE_SLICED, 2), small16, (unsigned)p.slices)
+                                        : go(MMB_KERNEL(false, MODE_SLICED, 2), small16, (unsigned)p.slices);
     else err = chains_in_split ? go(MMB_KERNEL(true, MODE_SLICED, TM), small, (unsigned)p.slices)
                                : go(MMB_KERNEL(false, MODE_SLICED, TM), small, (unsigned)p.slices);
     if (err != cudaSuccess) return err;
@@ -1041,7 +1088,7 @@ cudaError_t launch_staged_main(const Params& p, cudaStream_t stream, int* launch
     return err;
   }
   if (p.S > 1) err = p.fast ? go(MMB_KERNEL(false, MODE_PLAN, TM), small, 1) : go(MMB_KERNEL(true, MODE_PLAN, TM), large, 1);
-  else if (few_rows) err = p.fast ? go(MMB_KERNEL(false, MODE_ORDER, 2), small, 1) : go(MMB_KERNEL(true, MODE_ORDER, 2), large, 1);
+  else if (few_rows) err = p.fast ? go(MMB_KERNEL(false, MODE_ORDER, 2), small16, 1) : go(MMB_KERNEL(true, MODE_ORDER, 2), large16, 1);
   else err = p.fast ? go(MMB_KERNEL(false, MODE_ORDER, TM), small, 1) : go(MMB_KERNEL(true, MODE_ORDER, TM), large, 1);
 #undef MMB_KERNEL
   if (err == cudaSuccess) *launches += 1;
@@ -1125,17 +1172,7 @@ cudaError_t dispatch_formats(const Params& p, int nfma, cudaStream_t stream, boo
 // K slicing is worth its second pass when the output tiles leave most SMs idle; it aims at about two CTAs per SM.
 constexpr int SLICE_TILE_LIMIT = 74, SLICE_CTA_TARGET = 296;
 constexpr int ROW_GROUP_COST = 260;   // time of a 16-row CTA in thousandths of the time of a 128-row CTA over the same k
-// SMs of the current device (cached per device; 148 if the query fails).
-int sm_count() {
-  static std::atomic<int> cached[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  int n = cached[dev].load(std::memory_order_relaxed);
-  if (n > 0) return n;
-  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  cached[dev].store(n, std::memory_order_relaxed);
-  return n;
-}
+constexpr int ROW_GROUP_COST2 = 364;  // the same for two of them sharing an SM (each runs 1.4 times longer)
 constexpr size_t SLICE_SCRATCH_LIMIT = (size_t)4 << 30;
 
 struct WorkspaceLayout {
@@ -1294,7 +1331,8 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
     int slices = slices_for(rows16 ? tiles16 : tiles);
     // Row groups: when the 128 x 128 tiles and the chains of the plan leave most SMs without a CTA, the 16-row kernels
     // take the call -- up to eight CTAs per tile, each doing an eighth of a tile's work at about half the efficiency
-    // (ROW_GROUP_COST per mille of a tile's time). The estimate compares waves of CTAs on the device's SMs. The 16-row
+    // (ROW_GROUP_COST per mille of a tile's time), two of them per SM. The estimate compares waves of CTAs on the
+    // device's SMs. The 16-row
     // kernels walk unsplit plans in one pass and any plan in K slices, so a split plan needs at least two slices.
     if (!rows16 && !p.a_hp && !env_off("MMAEMU_B200_ROW_GROUPS")) {
       int s16 = slices_for(tiles16);
@@ -1302,9 +1340,13 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
           (size_t)tiles * (size_t)chains * TM * TN * THREADS * sizeof(float) <= wx.chains_bytes)
         s16 = 2;
       const long long sms = sm_count();
-      const long long waves8 = (tiles * slices + sms - 1) / sms, waves16 = (tiles16 * s16 + sms - 1) / sms;
+      const long long waves8 = (tiles * slices + sms - 1) / sms;
+      // two 16-row CTAs share an SM: a full double wave costs ROW_GROUP_COST2, a last wave of at most one CTA per SM
+      // ROW_GROUP_COST
+      const long long n16 = tiles16 * s16, pairs = n16 / (2 * sms), rest = n16 % (2 * sms);
+      const long long units16 = pairs * ROW_GROUP_COST2 + (rest == 0 ? 0 : (rest <= sms ? ROW_GROUP_COST : ROW_GROUP_COST2));
       // time in units of (one tile over all of K) / 1000: a slice does 1 / slices of it
-      const long long time8 = waves8 * 1000 / slices, time16 = waves16 * ROW_GROUP_COST / s16;
+      const long long time8 = waves8 * 1000 / slices, time16 = units16 / s16;
       if ((p.S == 1 || s16 >= 2) && time16 * 10 < time8 * 9) {
         rows16 = true;
         slices = s16;
