@@ -473,21 +473,21 @@ int mmb200_scaled_mm_host(const void* A, int64_t lda, int fmt_a, const void* B, 
                               (size_t)N * es, (size_t)N * es, (size_t)rows, cudaMemcpyDeviceToHost, sq);
       if (err != cudaSuccess) break;
     }
-    // back to the caller's stream: it continues when every internal stream is done (also after an error above, so
-    // that the staging memory is not freed under work that was already enqueued)
+  } while (0);
+  if (pipe) {
+    // back to the caller's stream: it continues when every internal stream is done -- also after an error above, so
+    // that the staging memory is not freed under work that was already enqueued
     for (int q = 0; q < HostPipeline::STREAMS; ++q) {
       cudaError_t e2 = cudaEventRecord(pipe->done[q], pipe->s[q]);
       if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, pipe->done[q], 0);
       if (e2 != cudaSuccess && err == cudaSuccess) err = e2;
     }
-    if (err != cudaSuccess || rc != MMB200_OK) break;
-    for (int i = 0; i < n_slabs; ++i) {                      // status words of the slabs' bounded waits
+    for (int i = 0; i < n_slabs && err == cudaSuccess && rc == MMB200_OK; ++i) {   // status words of the slabs' bounded waits
       const int m0 = i * slab_rows, rows = (M - m0 < slab_rows) ? M - m0 : slab_rows;
       err = cudaMemcpyAsync(&words[i], buf + w_off + (size_t)i * w_each + mmb::staged_status_offset(rows, N, K, S, true),
                             sizeof(int), cudaMemcpyDeviceToHost, st);
-      if (err != cudaSuccess) break;
     }
-  } while (0);
+  }
   cudaError_t ferr = cudaFreeAsync(buf, st);
   cudaError_t serr = cudaStreamSynchronize(st);   // the scales array and the caller's buffers must outlive the copies
   if (rc != MMB200_OK) return rc;
