@@ -1098,7 +1098,8 @@ cudaError_t launch_staged_main(const Params& p, cudaStream_t stream, int* launch
     else err = chains_in_split ? go(MMB_KERNEL(true, MODE_SLICED, TM), small, (unsigned)p.slices)
                                : go(MMB_KERNEL(false, MODE_SLICED, TM), small, (unsigned)p.slices);
     if (err != cudaSuccess) return err;
-    combine_kernel<<<dim3(tiles, TM * TN), THREADS, 0, stream>>>(p);
+    // one CTA per (tile, output slot of the first pass's threads); with at most 16 rows only the row slots 0 and 1 exist
+    combine_kernel<<<dim3(tiles, p.M <= 16 ? 2 * TN : TM * TN), THREADS, 0, stream>>>(p);
     err = cudaGetLastError();
     if (err == cudaSuccess) *launches += 2;
     return err;
