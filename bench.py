@@ -449,6 +449,19 @@ def other_configs(mm, oracle, timer, dev, issue_peak_t):
         c = dict(name=f"cfg3_{prof}_{M}x{N}x{K}", profile=prof, M=M, N=N, K=K, fa="e5m2", fb="e4m3", out=o, fast=fast,
                  splitk="auto")
         add(c, gaussian_codes(M, K, 8.0, 6 + i, "e5m2"), gaussian_codes(N, K, 8.0, 20 + i, "e4m3"), 2.0 ** -5, 2.0 ** -4)
+    # a prefill-like call with few rows and fast accumulation (one chain per output, 32 output tiles): the 16-row
+    # kernels take it by default (row groups); the same call with the switch off, for comparison
+    c = dict(name="rowgroups_hopper_64x4096x4096", profile="hopper", M=64, N=4096, K=4096, fa="e4m3", fb="e4m3",
+             out="bfloat16", fast=True, splitk=1)
+    ra, rb = gaussian_codes(64, 4096, 4.0, 60), gaussian_codes(4096, 4096, 4.0, 61)
+    add(c, ra, rb, 0.5, 1.25)
+    os.environ["MMAEMU_B200_ROW_GROUPS"] = "0"
+    try:
+        off = time_config(mm, oracle, timer, dev, dict(c, name="rowgroups_off"), ra, rb, 0.5, 1.25, 5)
+    finally:
+        os.environ.pop("MMAEMU_B200_ROW_GROUPS", None)
+    out[c["name"]]["ms_with_8_row_slot_kernels"] = off["ms"]
+    out[c["name"]]["kernel"] = "staged_tc_kernel, 16 rows per CTA (row groups)"
     # 4: FP8 projection stack, hopper-te, amax-derived scales
     for i, (N, K) in enumerate([(5760, 1920), (1920, 1920), (24576, 8192)]):
         M = 8192
