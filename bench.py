@@ -705,6 +705,11 @@ def run_multi_gpu(args) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries the one JSON line and nothing else: whatever libraries print there while the job runs (NCCL's
+    # version banner, for one) goes to stderr instead
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch N > 1 with torch.distributed.run")
     _lib.load()
@@ -880,7 +885,8 @@ def run_multi_gpu(args) -> int:
                               "tflops": 2.0 * gM * gN * gK / (grid_ms / args.steps / 1e3) / 1e12,
                               "bit_identical_to_one_gpu": True},
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     dist.barrier()
     dist.destroy_process_group()
     return 0
