@@ -27,9 +27,11 @@ static float code_value(uint32_t code, int fmt) {      // value of a sanitised c
   return s ? -v : v;
 }
 
-// POW: the block exponent comes from a sum of products of powers, as the tensor-core exponent pass computes it
-// (E4M3 x E4M3 only; here the sum is taken in k order with round-to-nearest fp32 additions).
-template <int FA, int FB, bool POW = false>
+// POW: the block exponent comes from sums of products of powers, as the tensor-core exponent pass computes it: 1 =
+// powers of 256, one sum per block (E4M3 x E4M3); 2 = powers of 32, the larger of the sums of 16 products (mixed
+// pairs). Here the sums are taken in k order with round-to-nearest fp32 additions, or -- every other block -- in
+// reverse order with truncation, since the result must not depend on either.
+template <int FA, int FB, int POW = 0>
 static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma, int chain_len, float* out) {
   using P = Pair<FA, FB>;
   const int Kp = (K + 31) / 32 * 32;
@@ -43,12 +45,14 @@ static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma
       for (int g = 0; g < nfma / 4; ++g) {
         uint32_t wa = 0, wb = 0, ws, xw, cls, pw;
         for (int q = 0; q < 4; ++q) { wa |= (uint32_t)pa[k0 + 4 * g + q] << (8 * q); wb |= (uint32_t)pb[k0 + 4 * g + q] << (8 * q); }
-        decode_bits<FA>(wa, XBIAS_A, P::TADD_A, P::TZERO_A, ws, xw, ta[g], sa[g], cls, &pw, POW_BIAS_A);
+        decode_bits<FA, POW == 2 ? 5 : 8>(wa, XBIAS_A, P::TADD_A, P::TZERO_A, ws, xw, ta[g], sa[g], cls, &pw,
+                                           POW == 2 ? POW5_BIAS : POW_BIAS_A);
         for (int q = 0; q < 4; ++q) {
           xa[4 * g + q] = (xw >> (8 * q)) & 0xFF; va[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FA);
           pwa[4 * g + q] = u2f(((pw >> (8 * q)) & 0xFF) << 23);
         }
-        decode_bits<FB>(wb, XBIAS_B, P::TADD_B, P::TZERO_B, ws, xw, tb[g], sb[g], cls, &pw, POW_BIAS_B);
+        decode_bits<FB, POW == 2 ? 5 : 8>(wb, XBIAS_B, P::TADD_B, P::TZERO_B, ws, xw, tb[g], sb[g], cls, &pw,
+                                           POW == 2 ? POW5_BIAS : POW_BIAS_B);
         for (int q = 0; q < 4; ++q) {
           xbv[4 * g + q] = (xw >> (8 * q)) & 0xFF; vb[4 * g + q] = code_value((ws >> (8 * q)) & 0xFF, FB);
           pwb[4 * g + q] = u2f(((pw >> (8 * q)) & 0xFF) << 23);
@@ -56,10 +60,19 @@ static void chains(const uint8_t* a, const uint8_t* b, int rows, int K, int nfma
       }
       uint32_t tt;
       float R, offset;
-      if (POW) {
+      if (POW == 1) {
         float S = 0.0f;
         for (int c = 0; c < nfma; ++c) S = add_rn(S, pwa[c] * pwb[c]);
         R = block_start_at<FA, FB>(acc, block_exponent_pow_raw(acc, S) | 0x12345u, tt, offset);   // low bits: any
+      } else if (POW == 2) {
+        float best = 0.0f;
+        for (int h = 0; h < nfma; h += 16) {
+          float S = 0.0f;
+          if ((k0 / nfma) & 1) { for (int c = h + 15; c >= h; --c) S = add_rz(S, pwa[c] * pwb[c]); }
+          else { for (int c = h; c < h + 16; ++c) S = add_rn(S, pwa[c] * pwb[c]); }
+          best = S > best ? S : best;
+        }
+        R = block_start_at<FA, FB>(acc, block_exponent_pow5_raw<FA, FB>(acc, best) | 0x12345u, tt, offset);
       } else {
         uint32_t e2 = 0;                                // this output in the high half, a dummy neighbour in the low half
         for (int c = 0; c < nfma; ++c) e2 = addmax16x2(xa[c] * 0x00010001u, (xbv[c] << 16) | 1u, e2);
@@ -83,7 +96,15 @@ extern "C" int fast_math_chains(const uint8_t* a, const uint8_t* b, int rows, in
                                 int chain_len, float* out) {
   if ((nfma != 16 && nfma != 32) || rows < 0 || K < 0 || (chain_len && chain_len % nfma)) return -1;
   if (fa == 4 && fb == 4) {                            // format code 4: E4M3 with the power-sum exponent pass
-    chains<FMT_E4M3, FMT_E4M3, true>(a, b, rows, K, nfma, chain_len, out);
+    chains<FMT_E4M3, FMT_E4M3, 1>(a, b, rows, K, nfma, chain_len, out);
+    return 0;
+  }
+  if (fa == 5 && fb == 4) {                            // 5: E5M2 with the power-sum exponent pass (mixed pairs: base 32)
+    chains<FMT_E5M2, FMT_E4M3, 2>(a, b, rows, K, nfma, chain_len, out);
+    return 0;
+  }
+  if (fa == 4 && fb == 5) {
+    chains<FMT_E4M3, FMT_E5M2, 2>(a, b, rows, K, nfma, chain_len, out);
     return 0;
   }
   switch (fa * 2 + fb) {
@@ -99,6 +120,60 @@ extern "C" int fast_math_chains(const uint8_t* a, const uint8_t* b, int rows, in
 // Checks block_exponent_pow for every block exponent E of E4M3 x E4M3 products and the extreme sums a tensor core
 // may return: the largest term alone, sums of 32 largest terms with slack, and random mixtures; then the power bytes of
 // decode_bits. Returns the number of failures.
+// Checks block_exponent_pow5_raw for every largest product exponent of both mixed pairs and the extreme 16-term sums a
+// tensor core may return (the largest term alone; 16 largest terms with rounding slack; random mixtures), with
+// accumulators above and below, and the power bytes of decode_bits for both formats. Returns the number of failures.
+template <int FA, int FB>
+static int pow5_check_pair() {
+  int bad = 0;
+  uint32_t rng = 777u;
+  const int eoff = F8<FA>::EOFF + F8<FB>::EOFF, smax = (FA == FMT_E5M2 ? 29 : 14) + (FB == FMT_E5M2 ? 29 : 14);
+  for (int S = 0; S <= smax; ++S) {
+    const int E = S - eoff;
+    const double top = std::ldexp(1.0, 5 + 5 * S - 127);
+    const uint32_t want = (uint32_t)(E + 127);
+    const double cand[5] = {top, top * 16.0, top * 17.0, top * 1.999, top * 15.99};
+    for (int c = 0; c < 5; ++c)
+      if ((block_exponent_pow5_raw<FA, FB>(0.0f, (float)cand[c]) >> 23) != want) ++bad;
+    for (int trial = 0; trial < 200; ++trial) {
+      double s = top;
+      for (int k = 0; k < 15; ++k) {
+        rng = rng * 1664525u + 1013904223u;
+        int e = S - (int)((rng >> 24) % 6);
+        if (e < 0) e = 0;
+        if ((rng >> 8) & 1) s += std::ldexp(1.0, 5 + 5 * e - 127);
+      }
+      if ((block_exponent_pow5_raw<FA, FB>(0.0f, (float)s) >> 23) != want) ++bad;
+      if ((block_exponent_pow5_raw<FA, FB>(std::ldexp(-1.5f, E + 3), (float)s) >> 23) != want + 3) ++bad;
+      if ((block_exponent_pow5_raw<FA, FB>(std::ldexp(1.99f, E - 1), (float)s) >> 23) != want) ++bad;
+    }
+  }
+  if ((block_exponent_pow5_raw<FA, FB>(0.0f, 0.0f) >> 23) != (uint32_t)(126 - eoff)) ++bad;
+  return bad;
+}
+
+extern "C" int fast_math_power5_check(void) {
+  int bad = pow5_check_pair<FMT_E5M2, FMT_E4M3>() + pow5_check_pair<FMT_E4M3, FMT_E5M2>();
+  // the division by 5 on the bit pattern, for every field and the mantissas that can occur
+  for (uint32_t field = 1; field <= 254; ++field)
+    for (uint32_t mant : {0u, 1u, 0x080000u, 0x7FFFFFu}) {
+      if (field % 5 == 4 && mant > 0x090000u) continue;         // a 16-term sum in its top binade stays below 1.07
+      if ((mulhi_u32((field << 23) | mant, 1639u) >> 4) != field / 5) ++bad;
+    }
+  for (uint32_t code = 0; code < 256; ++code) {
+    uint32_t ws, xb, tc, sg, cls, pw;
+    decode_bits<FMT_E5M2, 5>(code * 0x01010101u, XBIAS_A, 0, 35, ws, xb, tc, sg, cls, &pw, POW5_BIAS);
+    uint32_t m = code & 0x7F, e = m >> 2;
+    uint32_t want = (m == 0 || e == 31) ? 0u : POW5_BIAS + 5 * (e ? e - 1 : 0);
+    if (pw != want * 0x01010101u) ++bad;
+    decode_bits<FMT_E4M3, 5>(code * 0x01010101u, XBIAS_B, 0, 35, ws, xb, tc, sg, cls, &pw, POW5_BIAS);
+    m = code & 0x7F; e = m >> 3;
+    want = (m == 0 || m == 0x7F) ? 0u : POW5_BIAS + 5 * (e ? e - 1 : 0);
+    if (pw != want * 0x01010101u) ++bad;
+  }
+  return bad;
+}
+
 extern "C" int fast_math_power_sum_check(void) {
   int bad = 0;
   uint32_t rng = 12345u;

@@ -17,7 +17,7 @@ from oracle import oracle
 HERE = Path(__file__).resolve().parent
 SRC = HERE / "host" / "fast_math_host.cpp"
 LIB = HERE / "host" / "_build" / "libfast_math_host.so"
-FMT = {"e4m3": 0, "e5m2": 1, "e4m3-pow": 4}     # "e4m3-pow": block exponents from sums of powers (tensor-core pass)
+FMT = {"e4m3": 0, "e5m2": 1, "e4m3-pow": 4, "e5m2-pow": 5}     # "-pow": block exponents from sums of powers (tensor-core pass)
 
 
 @pytest.fixture(scope="module")
@@ -31,6 +31,7 @@ def lib():
     L.fast_math_chains.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_void_p]
     L.fast_math_chains.restype = ctypes.c_int
     L.fast_math_power_sum_check.restype = ctypes.c_int
+    L.fast_math_power5_check.restype = ctypes.c_int
     return L
 
 
@@ -69,6 +70,27 @@ def test_power_sum_exponent_pass_equals_the_block_model(lib, cls, nfma):
         if K >= 256:
             slow = np.array([oracle.accumulate(a[i:i + 1], b[i:i + 1], preset=nfma, fast=False)[0, 0] for i in range(8)])
             got = chains(lib, a[:8], b[:8], "e4m3-pow", "e4m3-pow", nfma, chain_len=128)
+            assert np.array_equal(got, slow), (cls, K)
+
+
+@pytest.mark.parametrize("nfma", (16, 32))
+@pytest.mark.parametrize("fmts", (("e5m2", "e4m3"), ("e4m3", "e5m2")), ids="x".join)
+@pytest.mark.parametrize("cls", datagen.CLASSES)
+def test_power_sum_exponent_pass_of_the_mixed_pairs(lib, cls, fmts, nfma):
+    """Mixed pairs: powers of 32 and the larger of the 16-term sums (block_exponent_pow5_raw), summed in two different
+    orders and rounding modes by the host harness."""
+    assert lib.fast_math_power5_check() == 0
+    rng = np.random.default_rng(len(cls) * 29 + nfma)
+    for K in (16, 48, 256, 1936, 8192):
+        a = datagen.codes(rng, 64, K, fmts[0], cls, 0)
+        b = datagen.codes(rng, 64, K, fmts[1], cls, 1)
+        want = oracle.dot(a, b, None, fmt_a=fmts[0], fmt_b=fmts[1], preset=nfma)
+        got = chains(lib, a, b, fmts[0] + "-pow", fmts[1] + "-pow", nfma)
+        assert np.array_equal(got, want), (cls, K)
+        if K >= 256:
+            slow = np.array([oracle.accumulate(a[i:i + 1], b[i:i + 1], fmt_a=fmts[0], fmt_b=fmts[1], preset=nfma,
+                                               fast=False)[0, 0] for i in range(8)])
+            got = chains(lib, a[:8], b[:8], fmts[0] + "-pow", fmts[1] + "-pow", nfma, chain_len=128)
             assert np.array_equal(got, slow), (cls, K)
 
 

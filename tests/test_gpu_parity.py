@@ -93,21 +93,24 @@ def test_late_accumulator_preset(gpu, cls, fmts):
 
 
 @pytest.mark.parametrize("preset", (16, 32))
+@pytest.mark.parametrize("fmts", (("e4m3", "e4m3"), ("e5m2", "e4m3"), ("e4m3", "e5m2")), ids="x".join)
 @pytest.mark.parametrize("cls", datagen.CLASSES)
-def test_packed_integer_exponent_pass_for_e4m3_pairs(gpu, cls, preset):
-    """E4M3 x E4M3 takes its exponent pass from the tensor cores by default; the packed-integer pass of the other format
-    pairs serves it too (MMAEMU_B200_TC_EPASS=0) and must give the same bits: chains, a slow-accumulation plan and a
-    split plan."""
-    rng = np.random.default_rng(zlib.crc32(repr((cls, preset, "int")).encode()))
-    for M, N, K in ((65, 63, 48), (200, 257, 1920)):
-        a = datagen.codes(rng, M, K, "e4m3", cls, 0)
-        b = datagen.codes(rng, N, K, "e4m3", cls, 1)
-        _same(gpu.chain(a, b, preset=preset, kernel="staged-int"), oracle.accumulate(a, b, preset=preset, fast=True),
+def test_packed_integer_exponent_pass_for_tensor_core_pairs(gpu, cls, preset, fmts):
+    """Every pair but E5M2 x E5M2 takes its exponent pass from the tensor cores by default (powers of 256 for
+    E4M3 x E4M3, powers of 32 and the larger of two 16-term sums for the mixed pairs); the packed-integer pass serves
+    them too (MMAEMU_B200_TC_EPASS=0) and must give the same bits: chains, a slow-accumulation plan and a split
+    plan, on the 8-row-slot kernels and on the 16-row kernels."""
+    rng = np.random.default_rng(zlib.crc32(repr((cls, preset, fmts, "int")).encode()))
+    f = dict(fmt_a=fmts[0], fmt_b=fmts[1])
+    for M, N, K in ((65, 63, 48), (200, 257, 1920), (9, 140, 1056)):
+        a = datagen.codes(rng, M, K, fmts[0], cls, 0)
+        b = datagen.codes(rng, N, K, fmts[1], cls, 1)
+        _same(gpu.chain(a, b, preset=preset, kernel="staged-int", **f), oracle.accumulate(a, b, preset=preset, fast=True, **f),
               f"{cls} {M}x{N}x{K}")
         sch = "contiguous" if preset == 32 else "pairwise"
         for kw in (dict(fast=False, S=1, scheme="none"), dict(fast=True, S=3, scheme=sch)):
-            _same(gpu.accumulate(a, b, preset=preset, kernel="staged-int", **kw), oracle.accumulate(a, b, preset=preset, **kw),
-                  f"{cls} {M}x{N}x{K} {kw}")
+            _same(gpu.accumulate(a, b, preset=preset, kernel="staged-int", **kw, **f),
+                  oracle.accumulate(a, b, preset=preset, **kw, **f), f"{cls} {M}x{N}x{K} {kw}")
 
 
 PLANS = ([(16, False, 1, "none"), (32, False, 1, "none")]
