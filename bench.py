@@ -51,7 +51,7 @@ STRONG = dict(name="cfg5_recipe_16384x16384x8192", profile="hopper", M=16384, N=
 # (smsp__inst_executed.sum * 32 / (M*N*K), profiles/): keyed by (kernel, products per block, accumulation). A workload
 # whose kernel has no capture gets no issue-slot roofline (null), never another kernel's constant.
 INST_PER_MAC = {("staged_tc_kernel", 32, "slow"): 2.514,       # 4096 cube, profiles/staged_tc_kernel_hopper_e4m3_2048cube.md
-                ("staged_kernel", 32, "slow"): 3.16,           # 2048 cube e5m2 x e4m3, profiles/staged_kernel_hopper_e5m2xe4m3_2048cube.md
+                ("staged_kernel", 32, "slow"): 3.16,           # 2048 cube e5m2 x e4m3 with MMAEMU_B200_TC_EPASS=0, profiles/staged_kernel_hopper_e5m2xe4m3_2048cube.md
                 ("fast_kernel", 32, "slow"): 3.37,             # 2048 cube, profiles/fast_kernel_hopper_e4m3_2048cube.md
                 ("staged_kernel, at most 16 rows", 32, "slow"): 5.18,   # 16 x 4096 x 8192, profiles/few_rows_kernel_hopper_e5m2xe4m3_16x4096x8192.md
                 ("integer_kernel", 32, "slow"): 8.56}           # 2048 cube, profiles/integer_kernel_hopper_e4m3_2048cube.md
@@ -314,7 +314,9 @@ def workload_text(c) -> str:
 
 def kernel_of(cfg, S=1) -> str:
     """Name of the main kernel the automatic choice runs for a configuration (with scratch memory)."""
-    name = "staged_tc_kernel" if (cfg["fa"], cfg["fb"]) == ("e4m3", "e4m3") else "staged_kernel"
+    pair = (cfg["fa"], cfg["fb"])
+    name = ("staged_tc_kernel" if pair == ("e4m3", "e4m3") else
+            "staged_kernel" if pair == ("e5m2", "e5m2") else "staged_tc_kernel, powers of 32")
     # with at most 16 rows (unsplit plans and K slices) the instantiations that decode both operands themselves run
     return name + ", at most 16 rows" if cfg["M"] <= 16 else name
 
