@@ -51,7 +51,7 @@ struct Params {
                          // themselves (set by the launcher: calls with at most 16 rows, and calls whose 128 x 128 output
                          // tiles and chains would leave most SMs idle)
   int row_groups;        // 16-row groups per 128-row tile in that case (grid z): 1 or 8
-  int no_tensor_epass;   // 1: the staged kernel keeps the exponent pass on the CUDA cores (E4M3 x E4M3 only matters)
+  int no_tensor_epass;   // 1: the staged kernels keep the exponent pass on the CUDA cores (packed integers) for every pair
   // multi-GPU assembly: the same output element is also stored at the same index of every peer_D[i] (device pointers
   // into other GPUs' memory, mapped into this process), so that every GPU ends up with the whole result
   void* peer_D[MMB200_MAX_PEERS];

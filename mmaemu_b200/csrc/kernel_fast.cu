@@ -1419,7 +1419,7 @@ cudaError_t launch_staged(const Params& p_in, int nfma, void* workspace, size_t 
   p.wait_polls = g_wait_polls.load();
   p.test_announce_extra = g_announce_extra.load();
   {
-    const char* env = std::getenv("MMAEMU_B200_TC_EPASS");         // "0": exponent pass of E4M3 x E4M3 on the CUDA cores too
+    const char* env = std::getenv("MMAEMU_B200_TC_EPASS");         // "0": the packed-integer exponent pass for every pair
     if (env && env[0] == '0' && env[1] == 0) p.no_tensor_epass = 1;
   }
   cudaError_t err = cudaMemsetAsync(base + w.flag_a, 0, w.seq - w.flag_a, stream);   // row flags and status word
