@@ -82,3 +82,13 @@ def test_no_device_is_a_status_not_a_crash(lib):
     assert rc in (_lib.ERR_LAUNCH, _lib.ERR_ARCH)
     if rc == _lib.ERR_LAUNCH:
         assert lib.mmb200_last_cuda_error().decode() != ""
+
+
+def test_preset_numbers_of_the_header_match_the_python_presets():
+    """The `nfma` argument names the preset: the header's MMB200_PRESET_* values are Preset.code of numerics.py."""
+    import re
+    from pathlib import Path
+    from mmaemu_b200.numerics import PRESETS
+    text = (Path(__file__).resolve().parents[1] / "include" / "mmaemu_b200.h").read_text()
+    header = {m.group(1).lower(): int(m.group(2)) for m in re.finditer(r"#define MMB200_PRESET_(\w+) (\d+)", text)}
+    assert header == {name: p.code for name, p in PRESETS.items()} == {"ada": 16, "hopper": 32, "b200_mma_sync": 288}
